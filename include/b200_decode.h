@@ -31,9 +31,11 @@ extern "C" {
 
 /* 2: + b200_engine_set_mailbox, b200_engine_generated;  3: + b200_sample_bf16, b200_sample_workspace_bytes,
  * b200_engine_set_sampler, b200_engine_options;  4: + layer-stack models (b200_stack_desc, b200_engine_create_stack),
- * sequence slots and the ragged step (b200_engine_step, b200_engine_slot_*), the per-mechanism stack ops.  All additive:
- * callers of an older version keep working. */
-#define B200_ABI_VERSION 5
+ * sequence slots and the ragged step (b200_engine_step, b200_engine_slot_*), the per-mechanism stack ops;  5: + sandwich
+ * blocks, latent attention, mLSTM, routed experts;  6: + post-norm blocks, the prepared attention (b200_attn_prep_desc), the
+ * generalized delta rule, Mamba-2, softmax-routed experts (fields appended to b200_moe_desc and b200_stack_layer),
+ * b200_stack_lin_scan, b200_stack_attn_prep.  All additive: callers of an older version keep working. */
+#define B200_ABI_VERSION 6
 
 typedef enum b200_status {
   B200_OK = 0,
@@ -292,15 +294,25 @@ int64_t b200_engine_bytes_per_token(const b200_engine* eng, int64_t ctx);
  * ---------------------------------------------------------------------------------------------------------------- */
 typedef enum b200_dtype { B200_BF16 = 0, B200_F32 = 1 } b200_dtype;
 /* PARALLEL: x += m·(mixer(h) + ff(h)), h = norm(x), one norm.  SANDWICH: x += post_norm(mixer(norm(x))), then
- * x += ff_post_norm(ff(ff_norm(x))) — a norm before and after every sublayer. */
-typedef enum b200_block_kind { B200_BLOCK_PARALLEL = 0, B200_BLOCK_SANDWICH = 1 } b200_block_kind;
-typedef enum b200_ff_act { B200_ACT_GELU_TANH = 0, B200_ACT_SILU = 1, B200_ACT_GELU_ERF = 2 } b200_ff_act;
+ * x += ff_post_norm(ff(ff_norm(x))) — a norm before and after every sublayer.  POSTNORM: x += post_norm(mixer(x)), then
+ * x += ff_post_norm(ff(x)) — the sublayers read the stream itself, the norm sits on their output only. */
+typedef enum b200_block_kind { B200_BLOCK_PARALLEL = 0, B200_BLOCK_SANDWICH = 1, B200_BLOCK_POSTNORM = 2 } b200_block_kind;
+/* RELU2: max(z, 0)²; TANH: tanh(z) (the bottleneck of a low-rank decay projection). */
+typedef enum b200_ff_act {
+  B200_ACT_GELU_TANH = 0, B200_ACT_SILU = 1, B200_ACT_GELU_ERF = 2, B200_ACT_RELU2 = 3, B200_ACT_TANH = 4
+} b200_ff_act;
 /* RMS: x·rsqrt(mean(x²) + eps)·(offset + w).  LAYER: (x − mean)·rsqrt(var + eps)·(offset + w), no bias. */
 typedef enum b200_norm_kind { B200_NORM_RMS = 0, B200_NORM_LAYER = 1 } b200_norm_kind;
 /* ATTENTION: the gated windowed attention of b200_attn_desc.  LATENT: keys and values expanded from a cached low-rank
  * latent + one rotated key part shared by the heads (b200_latent_desc).  MLSTM: a matrix memory per head carried from
- * token to token (b200_mlstm_desc); its state lives in fp32 beside the slot's caches. */
-typedef enum b200_mixer_kind { B200_MIX_ATTENTION = 0, B200_MIX_LATENT = 1, B200_MIX_MLSTM = 2 } b200_mixer_kind;
+ * token to token (b200_mlstm_desc); its state lives in fp32 beside the slot's caches.  DELTA: a key × value matrix per
+ * head with a per-channel decay and a rank-one removal along the unit key (b200_delta_desc).  MAMBA2: a short causal
+ * convolution and a scalar-decay state-space recurrence per head (b200_mamba_desc); the convolution's last inputs are part
+ * of the state.  In sandwich and post-norm blocks ATTENTION is the windowed attention of b200_attn_desc behind the
+ * per-token preparation of b200_attn_prep_desc (query / key norms, rotary positions, value norm, value mix-in). */
+typedef enum b200_mixer_kind {
+  B200_MIX_ATTENTION = 0, B200_MIX_LATENT = 1, B200_MIX_MLSTM = 2, B200_MIX_DELTA = 3, B200_MIX_MAMBA2 = 4
+} b200_mixer_kind;
 /* GATED: act(gate)·up → down (merged into w_in / w_out).  DENSE: act(up) → down.  MOE: routed clamped gated experts
  * (+ optional gated shared expert), b200_moe_desc. */
 typedef enum b200_ff_kind { B200_FF_GATED = 0, B200_FF_DENSE = 1, B200_FF_MOE = 2 } b200_ff_kind;
@@ -348,9 +360,61 @@ typedef struct b200_moe_desc {
   int32_t experts, top, expert_ff, shared_ff;
   float limit, shared_limit;
   const void* router;       /* [experts, width] */
-  const void* w_exp_in;     /* [experts][2·expert_ff, width]: gate rows, then up rows */
+  const void* w_exp_in;     /* [experts][2·expert_ff, width]: gate rows, then up rows (expert_act != 0: [experts][expert_ff, width]) */
   const void* w_exp_out;    /* [experts][width, expert_ff] */
+  /* variants (all 0: the form above) */
+  int32_t router_kind;      /* 0: weight = sigmoid(logit).  1: scores = softmax over all experts, the chosen scores are divided
+                             * by their sum (+ 1e-20) and multiplied by route_scale */
+  int32_t weight_output;    /* 0: the weight multiplies the expert's input, 1: its output */
+  int32_t expert_act;       /* 0: the clamped gated unit.  else a b200_ff_act applied to up·h alone (no gate rows, no clamp);
+                             * the shared expert has the same form: w_ff_in [up8(shared_ff), width] */
+  int32_t shared_plain;     /* 0: shared expert × sigmoid(sg·h).  1: added as it is (no gate row) */
+  float route_scale;
 } b200_moe_desc;
+
+/* What happens to q | k | v of an attention mixer between the in-projection and the cache, per token, in fp32:
+ *   qk_norm: q (all heads·dim entries at once) and k (all kv_heads·dim) are RMS-normed and multiplied by q_norm / k_norm;
+ *   rot_dims > 0: entry i < rot_dims/2 of every head of q and k is paired with entry i + rot_dims/2 and turned by the angle
+ *     whose {cos, sin} is rot_table[pos][i] (the entries from rot_dims on pass unchanged);
+ *   v_norm: every head's value is divided by its root mean square;
+ *   v_mix 1: this layer's values are kept for the later layers of the pass.  v_mix 2: v <- (1 − lambda)·v + lambda·(the values
+ *     the v_mix 1 layer kept for the same token), lambda read from mix_lambda on the device.
+ * What this leaves in the projection rows is what is cached and attended. */
+typedef struct b200_attn_prep_desc {
+  int32_t qk_norm, rot_dims, v_norm, v_mix;
+  const float* q_norm;      /* [heads·dim] */
+  const float* k_norm;      /* [kv_heads·dim] */
+  const float* rot_table;   /* [max_ctx][rot_dims/2][2] fp32 */
+  const float* mix_lambda;  /* [1] */
+} b200_attn_prep_desc;
+
+/* Generalized delta rule (sizes heads / dim / vdim in b200_attn_desc).  w_in rows [r | k | v | out gate: heads·vdim |
+ * removal logits: heads·dim | decay bottleneck: rank] at off_q / off_k / off_v / off_g / off_gate / off_up (the removal bias
+ * in b_in).  Per head and key channel: decay w = exp(−decay_scale·sigmoid(w2·tanh(bottleneck) + w0)), removal a =
+ * sigmoid(logit); u = k / sqrt(Σk² + unit_eps);  S_t = diag(w) S − (a∘u)(uᵀS) + k vᵀ (both terms read the old S), o = Sᵀr;
+ * then o / rms(o) per head · head_norm · sigmoid(out gate). */
+typedef struct b200_delta_desc {
+  int32_t rank;
+  float decay_scale, unit_eps;
+  const void* w2;           /* [heads·dim, up8(rank)] (padding columns zero) */
+  const float* w0;          /* [heads·dim] */
+  const float* head_norm;   /* [heads·vdim] */
+} b200_delta_desc;
+
+/* Mamba-2 (heads, vdim in b200_attn_desc; dim = state).  w_in rows [z: inner | x: inner | B: groups·state | C: groups·state
+ * | dt: heads] at off_g / off_v / off_k / off_q / off_gate, inner = heads·vdim; x | B | C are contiguous (off_k = off_v +
+ * inner, off_q = off_k + groups·state) and pass a causal convolution of `taps` taps per channel (conv_w [channels, taps],
+ * last column the current token's; conv_b) and SiLU.  dt = softplus(dt + dt_bias); per head (group h / (heads / groups)):
+ * S_t = exp(−exp(A_log)·dt) S + dt·B xᵀ, y = SᵀC + D x; then y·silu(z), an RMS norm in norm_groups equal parts, · norm. */
+typedef struct b200_mamba_desc {
+  int32_t state, groups, taps, norm_groups;
+  const float* conv_w;      /* [inner + 2·groups·state, taps] */
+  const float* conv_b;      /* [inner + 2·groups·state] */
+  const float* dt_bias;     /* [heads] */
+  const float* A_log;       /* [heads] */
+  const float* D;           /* [heads] */
+  const float* norm;        /* [inner] */
+} b200_mamba_desc;
 
 typedef struct b200_stack_layer {
   b200_attn_desc attn;
@@ -380,6 +444,9 @@ typedef struct b200_stack_layer {
   b200_latent_desc lat;
   b200_mlstm_desc rec;
   b200_moe_desc moe;
+  b200_attn_prep_desc prep;
+  b200_delta_desc delta;
+  b200_mamba_desc mamba;
 } b200_stack_layer;
 
 typedef struct b200_stack_desc {
@@ -468,6 +535,21 @@ int64_t b200_stack_mlstm_state_floats(int64_t heads, int64_t dim, int64_t vdim);
  * [rows, top]) and `scores` (fp32 [rows, top]) receive the routing when not NULL.  Synchronises (allocates its workspace). */
 int b200_stack_moe(float* y, const void* h, int64_t rows, int64_t width, const b200_moe_desc* moe, int32_t* chosen,
                    float* scores, int dtype, void* stream);
+/* The linear recurrence of n_seq sequences laid side by side (rows [row0[s], row0[s] + count[s]) in order), all operands fp32
+ * rows of stride ld: per head h and value column j, with s the dk entries of column j of S,
+ *   s <- d∘s − p·(q·s) + b·(v_j·vscale),  out[row, h·dv + j] = s·r.
+ * d [heads·dk] per row, or (d_scalar) [heads]; p, q [heads·dk] or both NULL (no removal); b, r [heads/share][dk] (`share`
+ * consecutive heads read one vector); v [heads·dv]; vscale [heads] or NULL.  State of a slot: [heads][dk][dv] fp32 at
+ * state + slot·slot_stride (slot / pos per ROW; a sequence whose first row has pos 0 starts from zero). */
+int b200_stack_lin_scan(float* out, const float* d, const float* p, const float* q, const float* b, const float* r, const float* v,
+                        const float* vscale, int64_t ld, int64_t heads, int64_t dk, int64_t dv, int64_t share, int64_t d_scalar,
+                        float* state, int64_t slot_stride, const int32_t* row0, const int32_t* count, const int32_t* slot,
+                        const int32_t* pos, int64_t n_seq, int64_t n_rows, void* stream);
+/* The preparation of an attention mixer's q | k | v (b200_attn_prep_desc), in place in proj's rows (row stride ld_proj, segments
+ * at off_q / off_k / off_v); vkeep (T [n_tok, ld_keep]) is written by a v_mix 1 layer and read by a v_mix 2 layer. */
+int b200_stack_attn_prep(void* proj, int64_t ld_proj, int64_t off_q, int64_t off_k, int64_t off_v, const int32_t* pos,
+                         int64_t n_tok, const b200_attn_desc* attn, const b200_attn_prep_desc* prep, void* vkeep,
+                         int64_t ld_keep, float eps, int dtype, void* stream);
 /* y[r, j] = T( min(g, limit)·sigmoid(1.702·min(g, limit))·(clamp(u, ±limit) + 1) ), g = gu[r, j], u = gu[r, n + j] */
 int b200_stack_glu_clamp(void* y, const void* gu, int64_t rows, int64_t n, float limit, int dtype, void* stream);
 

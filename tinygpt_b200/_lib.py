@@ -53,7 +53,25 @@ class MlstmDesc(C.Structure):
 class MoeDesc(C.Structure):
     _fields_ = [("experts", C.c_int32), ("top", C.c_int32), ("expert_ff", C.c_int32), ("shared_ff", C.c_int32),
                 ("limit", C.c_float), ("shared_limit", C.c_float),
-                ("router", C.c_void_p), ("w_exp_in", C.c_void_p), ("w_exp_out", C.c_void_p)]
+                ("router", C.c_void_p), ("w_exp_in", C.c_void_p), ("w_exp_out", C.c_void_p),
+                ("router_kind", C.c_int32), ("weight_output", C.c_int32), ("expert_act", C.c_int32),
+                ("shared_plain", C.c_int32), ("route_scale", C.c_float)]
+
+
+class AttnPrepDesc(C.Structure):
+    _fields_ = [("qk_norm", C.c_int32), ("rot_dims", C.c_int32), ("v_norm", C.c_int32), ("v_mix", C.c_int32),
+                ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("rot_table", C.c_void_p), ("mix_lambda", C.c_void_p)]
+
+
+class DeltaDesc(C.Structure):
+    _fields_ = [("rank", C.c_int32), ("decay_scale", C.c_float), ("unit_eps", C.c_float),
+                ("w2", C.c_void_p), ("w0", C.c_void_p), ("head_norm", C.c_void_p)]
+
+
+class MambaDesc(C.Structure):
+    _fields_ = [("state", C.c_int32), ("groups", C.c_int32), ("taps", C.c_int32), ("norm_groups", C.c_int32),
+                ("conv_w", C.c_void_p), ("conv_b", C.c_void_p), ("dt_bias", C.c_void_p), ("A_log", C.c_void_p),
+                ("D", C.c_void_p), ("norm", C.c_void_p)]
 
 
 class StackLayer(C.Structure):
@@ -66,7 +84,8 @@ class StackLayer(C.Structure):
                 ("mixer", C.c_int32), ("ff_kind", C.c_int32),
                 ("post_norm", C.c_void_p), ("ff_norm", C.c_void_p), ("ff_post_norm", C.c_void_p),
                 ("w_ff_in", C.c_void_p), ("w_ff_out", C.c_void_p),
-                ("lat", LatentDesc), ("rec", MlstmDesc), ("moe", MoeDesc)]
+                ("lat", LatentDesc), ("rec", MlstmDesc), ("moe", MoeDesc),
+                ("prep", AttnPrepDesc), ("delta", DeltaDesc), ("mamba", MambaDesc)]
 
 
 class StackDesc(C.Structure):
@@ -138,6 +157,8 @@ PROTOTYPES = {
     "b200_stack_mlstm_state_floats": (I64, [I64, I64, I64]),
     "b200_stack_moe": (I32, [P, P, I64, I64, C.POINTER(MoeDesc), P, P, I32, P]),
     "b200_stack_glu_clamp": (I32, [P, P, I64, I64, F, I32, P]),
+    "b200_stack_lin_scan": (I32, [P, P, P, P, P, P, P, P, I64, I64, I64, I64, I64, I64, P, I64, P, P, P, P, I64, I64, P]),
+    "b200_stack_attn_prep": (I32, [P, I64, I64, I64, I64, P, I64, C.POINTER(AttnDesc), C.POINTER(AttnPrepDesc), P, I64, F, I32, P]),
     "b200_tp_window_bytes": (I64, [C.POINTER(ModelDesc)]),
     "b200_tp_window_create": (I32, [I64, C.POINTER(P), C.c_char_p]),
     "b200_tp_window_open": (I32, [C.c_char_p, C.POINTER(P)]),

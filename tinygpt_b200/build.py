@@ -22,7 +22,7 @@ OBJ_DIR = LIB_DIR / "obj"
 LIB_PATH = LIB_DIR / "libb200decode.so"
 
 SOURCES = ["common.cu", "gemv.cu", "gemv_batch.cu", "gemm.cu", "prefill.cu", "prefill_attn.cu", "sampling.cu", "ops.cu", "attn.cu", "engine.cu", "api.cu", "tp.cu", "stack_ops.cu",
-           "stack_mix.cu", "engine_stack.cu"]
+           "stack_mix.cu", "stack_rec.cu", "engine_stack.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

@@ -1,6 +1,7 @@
 // api.cu — C-ABI entry points for the GEMV and the fused building blocks (declared in include/b200_decode.h).
 #include "gemv.cuh"
 #include "stack_mix.cuh"
+#include "stack_rec.cuh"
 #include <vector>
 #include "ops.cuh"
 #include "stack.cuh"
@@ -281,6 +282,37 @@ int b200_stack_moe(float* y, const void* h, int64_t rows, int64_t width, const b
   if (chosen) B200_CUDA(cudaMemcpyAsync(chosen, p.sel_e, P * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
   if (scores) B200_CUDA(cudaMemcpyAsync(scores, p.sel_w, P * 4, cudaMemcpyDeviceToDevice, (cudaStream_t)stream));
   return B200_OK;
+}
+
+int b200_stack_lin_scan(float* out, const float* d, const float* p, const float* q, const float* b, const float* r, const float* v,
+                        const float* vscale, int64_t ld, int64_t heads, int64_t dk, int64_t dv, int64_t share, int64_t d_scalar,
+                        float* state, int64_t slot_stride, const int32_t* row0, const int32_t* count, const int32_t* slot,
+                        const int32_t* pos, int64_t n_seq, int64_t n_rows, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(n_seq > 0 && n_rows >= n_seq && n_rows < (1 << 24) && heads > 0 && heads < (1 << 16) && dk > 0 && dv > 0 &&
+                     dv < (1 << 20),
+                 "stack_lin_scan: bad arguments");
+  b200::LinScan s;
+  s.heads = (int)heads; s.dk = (int)dk; s.dv = (int)dv; s.share = (int)share; s.d_scalar = (int)d_scalar;
+  s.d = d; s.p = p; s.q = q; s.b = b; s.r = r; s.v = v; s.vscale = vscale; s.ld = ld;
+  s.state = state; s.slot_stride = slot_stride;
+  s.seg_row0 = row0; s.seg_count = count; s.slot = slot; s.pos = pos; s.n_seg = (int)n_seq; s.n_tok = (int)n_rows;
+  s.o = out; s.ld_o = heads * dv;
+  return b200::launch_lin_scan(s, (cudaStream_t)stream);
+}
+
+int b200_stack_attn_prep(void* proj, int64_t ld_proj, int64_t off_q, int64_t off_k, int64_t off_v, const int32_t* pos,
+                         int64_t n_tok, const b200_attn_desc* attn, const b200_attn_prep_desc* prep, void* vkeep,
+                         int64_t ld_keep, float eps, int dtype, void* stream) {
+  int rc = b200_device_check();
+  if (rc != B200_OK) return rc;
+  B200_CHECK_ARG(attn && prep && n_tok > 0 && n_tok < (1 << 24), "stack_attn_prep: bad arguments");
+  b200::AttnPrep a;
+  a.a = *attn; a.d = *prep; a.eps = eps;
+  a.proj = proj; a.ld_proj = ld_proj; a.off_q = (int)off_q; a.off_k = (int)off_k; a.off_v = (int)off_v;
+  a.pos = pos; a.n_tok = (int)n_tok; a.vkeep = vkeep; a.ld_keep = ld_keep;
+  return b200::launch_attn_prep(a, dtype, (cudaStream_t)stream);
 }
 
 int b200_stack_glu_clamp(void* y, const void* gu, int64_t rows, int64_t n, float limit, int dtype, void* stream) {

@@ -26,6 +26,12 @@
 //        | Σ_chosen expert(score·h) + sigmoid(sg·h)·shared(h)    routed experts: rows sorted by expert, grouped products
 //   x   += norm(y)·ff_post_norm
 // and the logits may be soft-capped.
+//
+// Post-norm blocks are the same run without the norms in front: the sublayers read the stream itself (its T-typed copy),
+//   x += norm(mixer(x))·post_norm,   x += norm(ff(x))·ff_post_norm
+// with three more mixers: the windowed attention behind a per-token preparation of q | k | v (norms, rotary positions,
+// value mix-in), the generalized delta rule and Mamba-2 — two recurrences that share one scan kernel and keep their fp32
+// state (and the convolution's last inputs) in the slot, beside the caches of the attention runs.
 #include <algorithm>
 #include <cstring>
 #include <map>
@@ -34,6 +40,7 @@
 
 #include "engine.cuh"
 #include "stack_mix.cuh"
+#include "stack_rec.cuh"
 
 namespace b200 {
 
@@ -117,9 +124,13 @@ struct StackEngine {
   int qa_max = 0, ol_max = 0, rec_o_max = 0, moe_e_max = 0, moe_top_max = 0, moe_ff_max = 0, lin_max = 0;
   bool any_rec = false, any_moe = false;
   bool h_ready = false;            // the previous sublayer's fused post-norm already left this run's normed input in h
+  // ---- post-norm blocks: the scan's fp32 operand rows, the decay projection's two stages, the kept values of a pass
+  float *rec_f = nullptr, *rec_wl = nullptr;
+  void *rec_lr = nullptr, *vkeep = nullptr;
+  int rec_f_max = 0, rec_wl_max = 0, rec_lr_max = 0, vkeep_max = 0;
   struct SPlans {
-    GemvPlan in{}, out{}, ff_in{}, ff_out{};
-    bool ok_in = false, ok_out = false, ok_ff_in = false, ok_ff_out = false;
+    GemvPlan in{}, out{}, ff_in{}, ff_out{}, lora{};
+    bool ok_in = false, ok_out = false, ok_ff_in = false, ok_ff_out = false, ok_lora = false;
   };
   std::vector<SPlans> splans;
 };
@@ -198,7 +209,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_aws = take((size_t)kStackSplitRows * s->max_heads * kStackMaxSplits * (2 + s->max_vdim) * 4);
   const size_t o_tick = take((size_t)kStackSplitRows * s->max_heads * 4);
   // sandwich blocks
-  const bool sw = d.block == B200_BLOCK_SANDWICH;
+  const bool sw = d.block != B200_BLOCK_PARALLEL;
   const size_t o_qa = take(sw ? T * s->qa_max * s->esz : 0), o_ol = take(sw ? T * s->ol_max * s->esz : 0);
   const size_t o_lt = take(sw ? T * s->lin_max * 2 : 0);
   const size_t o_pf = take(s->any_rec ? (size_t)kMaxBatch * s->n_in_max * 4 + T * 2 * s->max_heads * 4 : 0);
@@ -216,6 +227,8 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_lc = take(lx ? C * s->lat_rank_max * 2 : 0), o_lkp = take(lx ? C * s->lat_hd_max * 2 : 0);
   const size_t o_lk = take(lx ? C * s->lat_hd_max * 2 : 0), o_lv = take(lx ? C * s->lat_hv_max * 2 : 0);
   const size_t o_lq = take(lx ? T * s->lat_hd_max * 2 : 0);
+  const size_t o_rf = take(T * s->rec_f_max * 4), o_rw = take(T * s->rec_wl_max * 4);
+  const size_t o_rl = take(T * s->rec_lr_max * s->esz), o_vk = take(T * s->vkeep_max * s->esz);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->lat_c = lx ? (__nv_bfloat16*)(s->ws + o_lc) : nullptr;
@@ -223,6 +236,10 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->lat_k = lx ? (__nv_bfloat16*)(s->ws + o_lk) : nullptr;
   s->lat_v = (__nv_bfloat16*)(s->ws + o_lv);
   s->lat_q = (__nv_bfloat16*)(s->ws + o_lq);
+  s->rec_f = (float*)(s->ws + o_rf);
+  s->rec_wl = (float*)(s->ws + o_rw);
+  s->rec_lr = s->ws + o_rl;
+  s->vkeep = s->ws + o_vk;
   s->ws_tok = tok;
   s->ws_rows = rows;
   s->x = (float*)(s->ws + o_x);
@@ -524,6 +541,10 @@ static int stack_lin(StackEngine* s, const void* A, const void* Wt, const float*
 static int stack_norm_add_next(StackEngine* s, float* x, const void* y, bool y_bf16, const float* norm_w, const float* next_w,
                                int M, cudaStream_t st) {
   const b200_stack_desc& d = s->d;
+  if (d.block == B200_BLOCK_POSTNORM)   // the next sublayer reads the stream itself: fp32 engines in place, bf16 engines the
+    return launch_stack_rms_add_cast(x, y, y_bf16, norm_w,   // copy this pass leaves in h (next_w only says there is one)
+                                     next_w != nullptr && s->dtype == B200_BF16 ? (__nv_bfloat16*)s->h : nullptr, M, d.width,
+                                     d.norm_eps, d.residual_mult, st);
   if (next_w != nullptr)
     return launch_stack_norm_add_norm(x, y, y_bf16, norm_w, s->h, next_w, M, d.width, d.norm_eps, d.norm_offset, d.residual_mult,
                                       d.norm_kind, s->dtype, st);
@@ -552,19 +573,108 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
   int rc;
   // every sublayer's post-norm hands the next sublayer its normed input in the same pass; only the first run norms alone
   const bool has_ff = !(L.ff_kind == B200_FF_DENSE && L.ff <= 0);
-  const float* next_run_w = r + 1 < d.n_runs ? s->layers[s->run_layer[r + 1]].norm : nullptr;
+  // sandwich blocks norm the stream in front of every sublayer; post-norm blocks hand the sublayer the stream itself —
+  // fp32 engines read it in place, bf16 engines its rounded copy in h (left there by the previous post-norm pass)
+  const bool pre = d.block == B200_BLOCK_SANDWICH;
+  const float* next_run_w = r + 1 < d.n_runs ? (pre ? s->layers[s->run_layer[r + 1]].norm : L.post_norm) : nullptr;
+  const void* hin = !pre && dt == B200_F32 ? (const void*)x : (const void*)s->h;
   // ---- mixer
-  if (!s->h_ready &&
-      (rc = launch_stack_norm(s->h, x, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
-    return rc;
+  if (pre) {
+    if (!s->h_ready &&
+        (rc = launch_stack_norm(s->h, x, L.norm, nullptr, n_tok, W, d.norm_eps, d.norm_offset, d.norm_kind, dt, st)) != B200_OK)
+      return rc;
+  } else if (dt == B200_BF16 && !s->h_ready) {
+    if ((rc = launch_stack_cast((__nv_bfloat16*)s->h, x, (int64_t)n_tok * W, st)) != B200_OK) return rc;
+  }
   s->h_ready = false;
-  const bool rec = L.mixer == B200_MIX_MLSTM;
+  // rows whose logits stay fp32 (an mLSTM's gates, Mamba-2's step sizes): the GEMV hands out its unrounded sums, the other
+  // paths run those rows again
+  const int n_f32 = L.mixer == B200_MIX_MLSTM ? 2 * L.attn.heads : L.mixer == B200_MIX_MAMBA2 ? L.attn.heads : 0;
   const bool gemv_in = s->fast && n_tok <= kMaxBatch && pl.ok_in;
-  // an mLSTM's gate logits stay fp32: the GEMV hands out its unrounded sums, the other paths run the gate rows again
-  if ((rc = stack_lin(s, s->h, L.w_in, L.b_in, n_tok, L.n_in, W, pl.ok_in ? &pl.in : nullptr, s->proj,
-                      rec && gemv_in ? s->projf : nullptr, st)) != B200_OK)
+  if ((rc = stack_lin(s, hin, L.w_in, L.b_in, n_tok, L.n_in, W, pl.ok_in ? &pl.in : nullptr, s->proj,
+                      n_f32 > 0 && gemv_in ? s->projf : nullptr, st)) != B200_OK)
     return rc;
-  if (L.mixer == B200_MIX_LATENT) {
+  const float* f32_rows = nullptr;   // [n_tok, ld_f32]: the fp32 logits of the n_f32 rows from off_gate on
+  int64_t ld_f32 = 0;
+  if (n_f32 > 0 && gemv_in) {
+    f32_rows = s->projf + L.off_gate; ld_f32 = L.n_in;
+  } else if (n_f32 > 0) {
+    float* gates = s->projf + (size_t)kMaxBatch * s->n_in_max;
+    const void* wg = (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz;
+    const float* bg = L.b_in ? L.b_in + L.off_gate : nullptr;
+    if (n_tok <= kSmallRows) {
+      SmallGemv g;
+      g.a = hin; g.lda = W; g.w = wg; g.bias = bg;
+      g.c = gates; g.ldc = n_f32; g.c_f32 = true; g.M = n_tok; g.N = n_f32; g.K = W; g.items = 1;
+      if ((rc = launch_small_gemv(g, dt, st)) != B200_OK) return rc;
+    } else if ((rc = launch_skinny_f32(gates, hin, wg, bg, n_tok, n_f32, W, dt, st)) != B200_OK) {
+      return rc;
+    }
+    f32_rows = gates; ld_f32 = n_f32;
+  }
+  // the step's sequences for the recurrences (decode steps: every row is a sequence)
+  LinScan seq;
+  seq.slot = s->m_slot; seq.pos = s->m_pos; seq.n_tok = n_tok; seq.n_seg = n_tok;
+  if (!s->segs.empty()) {
+    seq.n_seg = (int)s->segs.size(); seq.seg_row0 = s->m_seg_row0; seq.seg_count = s->m_seg_count;
+  }
+  if (L.mixer == B200_MIX_ATTENTION) {
+    if (L.prep.qk_norm || L.prep.rot_dims > 0 || L.prep.v_norm || L.prep.v_mix) {
+      AttnPrep ap;
+      ap.a = L.attn; ap.d = L.prep; ap.eps = d.norm_eps;
+      ap.proj = s->proj; ap.ld_proj = L.n_in; ap.off_q = L.off_q; ap.off_k = L.off_k; ap.off_v = L.off_v;
+      ap.pos = s->m_pos; ap.n_tok = n_tok; ap.vkeep = s->vkeep; ap.ld_keep = s->vkeep_max;
+      if ((rc = launch_attn_prep(ap, dt, st)) != B200_OK) return rc;
+    }
+    StackAttn a;
+    a.a = L.attn;
+    a.proj = s->proj; a.ld_proj = L.n_in;
+    a.off_q = L.off_q; a.off_k = L.off_k; a.off_v = L.off_v; a.off_g = L.off_g;
+    a.kcache = s->kbase + s->run_k_off[r] * esz;
+    a.vcache = s->vbase + s->run_v_off[r] * esz;
+    a.k_slot_stride = (int64_t)s->k_slot; a.v_slot_stride = (int64_t)s->v_slot;
+    a.slot = s->m_slot; a.pos = s->m_pos; a.n_tok = n_tok;
+    a.out = s->mid; a.ld_out = L.k_out;
+    bool single = true;   // decode steps append K/V inside the attention launch
+    for (const StackEngine::Seg& g : s->segs) single = single && g.count == 1;
+    a.own_from_proj = single ? 1 : 0;
+    if (!a.own_from_proj && (rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
+    if ((rc = stack_attention(s, a, L, st)) != B200_OK) return rc;
+  } else if (L.mixer == B200_MIX_DELTA) {
+    const int H = L.attn.heads, hd = H * L.attn.dim, rk = up8i(L.delta.rank);
+    // decay logits: tanh of the bottleneck rows (T), then w2·(…) + w0 in fp32
+    if ((rc = launch_stack_act_mul(s->rec_lr, rk, (const uint8_t*)s->proj + (size_t)L.off_up * esz, nullptr, L.n_in, n_tok, rk,
+                                   B200_ACT_TANH, dt, st)) != B200_OK)
+      return rc;
+    if ((rc = stack_lin(s, s->rec_lr, L.delta.w2, L.delta.w0, n_tok, hd, rk, pl.ok_lora ? &pl.lora : nullptr, nullptr, s->rec_wl,
+                        st)) != B200_OK)
+      return rc;
+    DeltaRun m;
+    m.a = L.attn; m.d = L.delta; m.eps = d.norm_eps;
+    m.proj = s->proj; m.ld_proj = L.n_in;
+    m.off_r = L.off_q; m.off_k = L.off_k; m.off_v = L.off_v; m.off_g = L.off_g; m.off_a = L.off_gate;
+    m.wl = s->rec_wl; m.f = s->rec_f;
+    m.scan = seq;
+    m.scan.ld = delta_row_floats(H, L.attn.dim, L.attn.vdim);
+    m.scan.state = s->rstate + s->run_s_off[r]; m.scan.slot_stride = (int64_t)s->s_slot;
+    m.scan.o = s->rec_o; m.scan.ld_o = (int64_t)H * L.attn.vdim;
+    m.mid = s->mid; m.ld_mid = L.k_out;
+    if ((rc = run_delta(m, dt, st)) != B200_OK) return rc;
+  } else if (L.mixer == B200_MIX_MAMBA2) {
+    const int H = L.attn.heads;
+    MambaRun m;
+    m.a = L.attn; m.m = L.mamba; m.eps = d.norm_eps;
+    m.proj = s->proj; m.ld_proj = L.n_in; m.off_z = L.off_g; m.off_x = L.off_v;
+    m.dt = f32_rows; m.ld_dt = ld_f32;
+    m.f = s->rec_f;
+    m.scan = seq;
+    m.scan.ld = mamba_row_floats(H, L.attn.vdim, L.mamba.state, L.mamba.groups);
+    m.scan.state = s->rstate + s->run_s_off[r]; m.scan.slot_stride = (int64_t)s->s_slot;
+    m.conv_state = m.scan.state + (size_t)H * L.mamba.state * L.attn.vdim;
+    m.scan.o = s->rec_o; m.scan.ld_o = (int64_t)H * L.attn.vdim;
+    m.mid = s->mid; m.ld_mid = L.k_out;
+    if ((rc = run_mamba(m, dt, st)) != B200_OK) return rc;
+  } else if (L.mixer == B200_MIX_LATENT) {
     LatentRun a;
     a.a = L.attn; a.l = L.lat; a.eps = d.norm_eps;
     a.proj = s->proj; a.ld_proj = L.n_in; a.off_q = L.off_q; a.off_down = L.off_k;
@@ -619,26 +729,10 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
       }
     }
   } else {
-    const int H = L.attn.heads;
     MlstmRun m;
     m.a = L.attn; m.gate_cap = L.rec.gate_cap; m.eps = d.norm_eps;
     m.proj = s->proj; m.ld_proj = L.n_in; m.off_q = L.off_q; m.off_k = L.off_k; m.off_v = L.off_v; m.off_g = L.off_g;
-    if (gemv_in) {
-      m.gates = s->projf + L.off_gate; m.ld_gates = L.n_in;
-    } else {
-      float* gates = s->projf + (size_t)kMaxBatch * s->n_in_max;
-      if (n_tok <= kSmallRows) {
-        SmallGemv g;
-        g.a = s->h; g.lda = W; g.w = (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz;
-        g.bias = L.b_in ? L.b_in + L.off_gate : nullptr;
-        g.c = gates; g.ldc = 2 * H; g.c_f32 = true; g.M = n_tok; g.N = 2 * H; g.K = W; g.items = 1;
-        if ((rc = launch_small_gemv(g, dt, st)) != B200_OK) return rc;
-      } else if ((rc = launch_skinny_f32(gates, s->h, (const uint8_t*)L.w_in + (size_t)L.off_gate * W * esz,
-                                         L.b_in ? L.b_in + L.off_gate : nullptr, n_tok, 2 * H, W, dt, st)) != B200_OK) {
-        return rc;
-      }
-      m.gates = gates; m.ld_gates = 2 * H;
-    }
+    m.gates = f32_rows; m.ld_gates = ld_f32;
     m.state = s->rstate + s->run_s_off[r]; m.slot_stride = (int64_t)s->s_slot;
     m.slot = s->m_slot; m.pos = s->m_pos; m.n_tok = n_tok;
     if (s->segs.empty()) {
@@ -650,7 +744,7 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     if ((rc = run_mlstm(m, dt, st)) != B200_OK) return rc;
   }
   if ((rc = stack_lin_norm_add(s, s->mid, L.w_out, n_tok, L.k_out, pl.ok_out ? &pl.out : nullptr, L.post_norm, x,
-                               has_ff ? L.ff_norm : next_run_w, st)) != B200_OK)
+                               has_ff ? (pre ? L.ff_norm : L.post_norm) : next_run_w, st)) != B200_OK)
     return rc;
   // ---- feed-forward
   if (!has_ff) {
@@ -659,31 +753,37 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
   }
   s->h_ready = next_run_w != nullptr;
   if (L.ff_kind == B200_FF_DENSE) {
-    if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, L.ff, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
+    if ((rc = stack_lin(s, hin, L.w_ff_in, nullptr, n_tok, L.ff, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
       return rc;
     if ((rc = launch_stack_act_mul(s->mid, L.ff, s->proj, nullptr, L.ff, n_tok, L.ff, L.ff_act, dt, st)) != B200_OK) return rc;
     return stack_lin_norm_add(s, s->mid, L.w_ff_out, n_tok, L.ff, pl.ok_ff_out ? &pl.ff_out : nullptr, L.ff_post_norm, x,
                               next_run_w, st);
   }
   MoeRun m = s->moe_ws;
-  m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = s->h; m.y = s->y;
+  m.m = L.moe; m.width = W; m.n_tok = n_tok; m.h = hin; m.y = s->y;
   m.small = n_tok <= kSmallRows;
   m.plan_stride = s->moe_e_max;
-  m.tc = s->fast && n_tok >= kGemmRows && gemm_shape_ok(2 * L.moe.expert_ff, W) && gemm_shape_ok(W, L.moe.expert_ff);
+  m.tc = s->fast && n_tok >= kGemmRows && gemm_shape_ok((L.moe.expert_act != 0 ? 1 : 2) * L.moe.expert_ff, W) &&
+         gemm_shape_ok(W, L.moe.expert_ff);
   if (m.tc) {   // that path reads the group sizes back: not inside a stream capture
     cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
     B200_CUDA(cudaStreamIsCapturing(st, &cs));
     m.tc = cs == cudaStreamCaptureStatusNone;
   }
   if (L.moe.shared_ff > 0) {
-    const int fs = L.moe.shared_ff, n_sh = up8i(2 * fs + 1);
-    if ((rc = stack_lin(s, s->h, L.w_ff_in, nullptr, n_tok, n_sh, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
+    const bool plain = L.moe.expert_act != 0;   // up alone behind a plain activation, no gate row
+    const int fs = L.moe.shared_ff, n_sh = plain ? up8i(fs) : up8i(2 * fs + 1);
+    if ((rc = stack_lin(s, hin, L.w_ff_in, nullptr, n_tok, n_sh, W, pl.ok_ff_in ? &pl.ff_in : nullptr, s->proj, nullptr, st)) != B200_OK)
       return rc;
-    if ((rc = launch_stack_glu_clamp(s->mid, fs, s->proj, n_sh, n_tok, fs, L.moe.shared_limit, dt, st)) != B200_OK) return rc;
+    if (plain) rc = launch_stack_act_mul(s->mid, fs, s->proj, nullptr, n_sh, n_tok, fs, L.moe.expert_act, dt, st);
+    else rc = launch_stack_glu_clamp(s->mid, fs, s->proj, n_sh, n_tok, fs, L.moe.shared_limit, dt, st);
+    if (rc != B200_OK) return rc;
     if ((rc = stack_lin(s, s->mid, L.w_ff_out, nullptr, n_tok, W, fs, pl.ok_ff_out ? &pl.ff_out : nullptr, nullptr, s->y2, st)) != B200_OK)
       return rc;
     m.shared = s->y2; m.shared_f32 = true;
-    m.sg = (const uint8_t*)s->proj + (size_t)2 * fs * esz; m.ld_sg = n_sh;
+    if (!L.moe.shared_plain) {
+      m.sg = (const uint8_t*)s->proj + (size_t)2 * fs * esz; m.ld_sg = n_sh;
+    }
   }
   if ((rc = run_moe(m, dt, st)) != B200_OK) return rc;
   return stack_norm_add_next(s, x, s->y, false, L.ff_post_norm, next_run_w, n_tok, st);
@@ -711,7 +811,7 @@ static int stack_pass(b200_engine* e, int n_tok, int n_rows, cudaStream_t st, bo
   }
   for (int r = 0; r < d.n_runs; ++r) {
     const b200_stack_layer& L = s->layers[s->run_layer[r]];
-    if (d.block == B200_BLOCK_SANDWICH) {
+    if (d.block != B200_BLOCK_PARALLEL) {
       if ((rc = stack_run_sandwich(s, r, cur, n_tok, st)) != B200_OK) return rc;
       continue;
     }
@@ -1023,11 +1123,20 @@ int64_t stack_bytes_per_token(const b200_engine* e, int64_t ctx) {
     bytes += ((int64_t)L.n_in * d.width + (int64_t)d.width * L.k_out) * s->esz;
     if (d.block == B200_BLOCK_SANDWICH) {
       const b200_attn_desc& a = L.attn;
-      if (L.mixer == B200_MIX_LATENT)   // uk, uv, the cache rows read once and one written
+      if (L.mixer == B200_MIX_ATTENTION) {
+        int64_t keys = ctx + 1;
+        if (a.window > 0) keys = std::min<int64_t>(keys, (int64_t)a.window + a.keep_first);
+        bytes += (keys + 1) * a.kv_heads * (a.dim + a.vdim) * s->esz;
+      } else if (L.mixer == B200_MIX_DELTA) {   // the decay's second stage; the state read and written
+        bytes += (int64_t)a.heads * a.dim * L.delta.rank * s->esz + 2ll * a.heads * a.dim * a.vdim * 4;
+      } else if (L.mixer == B200_MIX_MAMBA2) {
+        bytes += 2 * mamba_state_floats(a.heads, a.vdim, L.mamba.state, L.mamba.groups, L.mamba.taps) * 4;
+      } else if (L.mixer == B200_MIX_LATENT)   // uk, uv, the cache rows read once and one written
         bytes += ((int64_t)a.heads * (a.dim + a.vdim) * L.lat.kv_rank + (ctx + 2) * (L.lat.kv_rank + L.lat.rot_dim)) * s->esz;
       else                              // the state read and written
         bytes += 2 * mlstm_state_floats(a.heads, a.dim, a.vdim) * 4;
       if (L.ff_kind == B200_FF_DENSE) bytes += 2ll * L.ff * d.width * s->esz;
+      else if (L.moe.expert_act != 0) bytes += ((int64_t)L.moe.experts + 2ll * L.moe.top * L.moe.expert_ff + 2ll * L.moe.shared_ff) * d.width * s->esz;
       else bytes += ((int64_t)L.moe.experts + 3ll * L.moe.top * L.moe.expert_ff + 3ll * L.moe.shared_ff + 1) * d.width * s->esz;
       continue;
     }
@@ -1047,11 +1156,13 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   if (rc != B200_OK) return rc;
   const b200_stack_desc& d = *desc;
   B200_CHECK_ARG(d.dtype == B200_BF16 || d.dtype == B200_F32, "engine_create_stack: unknown dtype %d", d.dtype);
-  B200_CHECK_ARG(d.block == B200_BLOCK_PARALLEL || d.block == B200_BLOCK_SANDWICH, "engine_create_stack: block kind %d not built",
-                 d.block);
+  B200_CHECK_ARG(d.block == B200_BLOCK_PARALLEL || d.block == B200_BLOCK_SANDWICH || d.block == B200_BLOCK_POSTNORM,
+                 "engine_create_stack: block kind %d not built", d.block);
+  B200_CHECK_ARG(d.block != B200_BLOCK_POSTNORM || d.norm_kind == B200_NORM_RMS,
+                 "engine_create_stack: post-norm blocks are built with RMS norms");
   B200_CHECK_ARG(d.norm_kind == B200_NORM_RMS || d.norm_kind == B200_NORM_LAYER, "engine_create_stack: norm kind %d not built",
                  d.norm_kind);
-  B200_CHECK_ARG(d.block == B200_BLOCK_SANDWICH || d.norm_kind == B200_NORM_RMS,
+  B200_CHECK_ARG(d.block != B200_BLOCK_PARALLEL || d.norm_kind == B200_NORM_RMS,
                  "engine_create_stack: parallel blocks are built with RMS norms");
   B200_CHECK_ARG(d.logit_softcap >= 0.f, "engine_create_stack: negative logit_softcap");
   B200_CHECK_ARG(d.width > 0 && d.vocab > 0 && d.n_layers > 0 && d.n_runs > 0 && d.max_ctx > 0 && d.max_slots > 0,
@@ -1081,16 +1192,61 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   s->run_mix.assign(d.run_mix_host, d.run_mix_host + d.n_runs);
   s->d.layers_host = nullptr;
   s->d.run_layer_host = s->d.run_mix_host = nullptr;
-  const bool sandwich = d.block == B200_BLOCK_SANDWICH;
+  const bool sandwich = d.block != B200_BLOCK_PARALLEL;   // a norm per sublayer: in front and behind, or behind only
   for (int l = 0; sandwich && l < d.n_layers; ++l) {
     const b200_stack_layer& L = s->layers[l];
     const b200_attn_desc& a = L.attn;
     const int W = d.width;
-    B200_CHECK_ARG(L.mixer == B200_MIX_LATENT || L.mixer == B200_MIX_MLSTM, "engine_create_stack: layer %d: mixer kind %d is not built for sandwich blocks", l, L.mixer);
+    B200_CHECK_ARG(L.mixer >= B200_MIX_ATTENTION && L.mixer <= B200_MIX_MAMBA2, "engine_create_stack: layer %d: mixer kind %d is not built", l, L.mixer);
     B200_CHECK_ARG(a.heads > 0 && a.dim > 0 && a.vdim > 0, "engine_create_stack: layer %d: bad mixer sizes", l);
-    B200_CHECK_ARG(L.norm && L.post_norm && L.w_in && L.w_out && L.n_in > 0 && L.k_out == a.heads * a.vdim,
+    B200_CHECK_ARG((L.norm || d.block == B200_BLOCK_POSTNORM) && L.post_norm && L.w_in && L.w_out && L.n_in > 0 &&
+                       L.k_out == a.heads * a.vdim,
                    "engine_create_stack: layer %d: null weight or k_out != heads·vdim", l);
-    if (L.mixer == B200_MIX_LATENT) {
+    if (L.mixer == B200_MIX_ATTENTION) {
+      const b200_attn_prep_desc& q = L.prep;
+      B200_CHECK_ARG(a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.window >= 0 && a.keep_first >= 0 && a.vdim <= 256 && a.dim <= 1024,
+                     "engine_create_stack: layer %d: bad attention sizes", l);
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.kv_heads * a.dim <= L.n_in &&
+                         L.off_v + a.kv_heads * a.vdim <= L.n_in && (!a.out_gate || L.off_g + a.heads <= L.n_in),
+                     "engine_create_stack: layer %d: segment offsets do not fit", l);
+      B200_CHECK_ARG(q.rot_dims >= 0 && q.rot_dims % 2 == 0 && q.rot_dims <= a.dim && (q.rot_dims == 0 || q.rot_table) &&
+                         (!q.qk_norm || (q.q_norm && q.k_norm)) && q.v_mix >= 0 && q.v_mix <= 2 && (q.v_mix != 2 || q.mix_lambda),
+                     "engine_create_stack: layer %d: attention preparation", l);
+      if (q.v_mix) {
+        B200_CHECK_ARG(s->vkeep_max == 0 || s->vkeep_max == a.kv_heads * a.vdim,
+                       "engine_create_stack: layer %d: layers that mix values need equal value sizes", l);
+        B200_CHECK_ARG((q.v_mix == 1) == (s->vkeep_max == 0), "engine_create_stack: layer %d: the first value-mixing layer keeps, the later ones mix", l);
+        s->vkeep_max = a.kv_heads * a.vdim;
+      }
+      s->max_vdim = std::max(s->max_vdim, a.vdim);
+    } else if (L.mixer == B200_MIX_DELTA) {
+      const b200_delta_desc& q = L.delta;
+      B200_CHECK_ARG(a.dim <= kScanMaxDim && q.rank > 0 && q.w2 && q.w0 && q.head_norm && q.unit_eps >= 0.f,
+                     "engine_create_stack: layer %d: delta-rule description", l);
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.heads * a.dim <= L.n_in &&
+                         L.off_v + a.heads * a.vdim <= L.n_in && L.off_g + a.heads * a.vdim <= L.n_in &&
+                         L.off_gate + a.heads * a.dim <= L.n_in && L.off_up + up8i(q.rank) <= L.n_in,
+                     "engine_create_stack: layer %d: segment offsets do not fit", l);
+      s->rec_o_max = std::max(s->rec_o_max, a.heads * a.vdim);
+      s->rec_f_max = std::max(s->rec_f_max, (int)delta_row_floats(a.heads, a.dim, a.vdim));
+      s->rec_wl_max = std::max(s->rec_wl_max, a.heads * a.dim);
+      s->rec_lr_max = std::max(s->rec_lr_max, up8i(q.rank));
+      s->lin_max = std::max(s->lin_max, a.heads * a.dim);
+      s->any_rec = s->recurrent = true;
+    } else if (L.mixer == B200_MIX_MAMBA2) {
+      const b200_mamba_desc& q = L.mamba;
+      B200_CHECK_ARG(q.state > 0 && q.state <= kScanMaxDim && q.groups > 0 && a.heads % q.groups == 0 && q.taps >= 1 &&
+                         q.taps <= kMambaMaxTaps && q.norm_groups > 0 && (a.heads * a.vdim) % q.norm_groups == 0 && a.dim == q.state,
+                     "engine_create_stack: layer %d: Mamba-2 sizes (state 1 … %d, 1 … %d taps, groups dividing the heads)", l,
+                     kScanMaxDim, kMambaMaxTaps);
+      B200_CHECK_ARG(q.conv_w && q.conv_b && q.dt_bias && q.A_log && q.D && q.norm, "engine_create_stack: layer %d: null Mamba-2 weight", l);
+      B200_CHECK_ARG(L.off_g >= 0 && L.off_g + a.heads * a.vdim <= L.n_in &&
+                         L.off_v + a.heads * a.vdim + 2 * q.groups * q.state <= L.n_in && L.off_gate + a.heads <= L.n_in,
+                     "engine_create_stack: layer %d: segment offsets do not fit", l);
+      s->rec_o_max = std::max(s->rec_o_max, a.heads * a.vdim);
+      s->rec_f_max = std::max(s->rec_f_max, (int)mamba_row_floats(a.heads, a.vdim, q.state, q.groups));
+      s->any_rec = s->recurrent = true;
+    } else if (L.mixer == B200_MIX_LATENT) {
       const b200_latent_desc& q = L.lat;
       B200_CHECK_ARG(q.kv_rank > 0 && q.kv_rank <= kLatentMaxRank && q.rot_dim >= 0 && q.rot_dims >= 0 && q.rot_dims <= q.rot_dim &&
                          q.rot_dims % 2 == 0,
@@ -1106,6 +1262,7 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       s->lat_hd_max = std::max(s->lat_hd_max, a.heads * (a.dim + q.rot_dim));
       s->lat_hv_max = std::max(s->lat_hv_max, a.heads * a.vdim);
     } else {
+      B200_CHECK_ARG(L.mixer == B200_MIX_MLSTM, "engine_create_stack: layer %d: mixer kind %d", l, L.mixer);
       B200_CHECK_ARG(a.dim <= kMlstmMaxDim && L.rec.gate_cap > 0.f && L.rec.head_norm, "engine_create_stack: layer %d: mLSTM description", l);
       B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.heads * a.dim <= L.n_in &&
                          L.off_v + a.heads * a.vdim <= L.n_in && L.off_g + a.heads * a.vdim <= L.n_in &&
@@ -1116,22 +1273,27 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
     }
     int ff_rows = 0, ff_mid = 0;
     if (L.ff_kind == B200_FF_DENSE) {
-      B200_CHECK_ARG(L.ff >= 0 && (L.ff == 0 || (L.ff_norm && L.ff_post_norm && L.w_ff_in && L.w_ff_out)),
+      B200_CHECK_ARG(L.ff >= 0 && (L.ff == 0 || ((L.ff_norm || d.block == B200_BLOCK_POSTNORM) && L.ff_post_norm && L.w_ff_in && L.w_ff_out)),
                      "engine_create_stack: layer %d: dense feed-forward", l);
-      B200_CHECK_ARG(L.ff_act == B200_ACT_GELU_TANH || L.ff_act == B200_ACT_SILU || L.ff_act == B200_ACT_GELU_ERF,
-                     "engine_create_stack: layer %d: activation %d", l, L.ff_act);
+      B200_CHECK_ARG(L.ff_act >= B200_ACT_GELU_TANH && L.ff_act <= B200_ACT_TANH, "engine_create_stack: layer %d: activation %d", l,
+                     L.ff_act);
       ff_rows = ff_mid = L.ff;
     } else {
       const b200_moe_desc& m = L.moe;
       B200_CHECK_ARG(L.ff_kind == B200_FF_MOE, "engine_create_stack: layer %d: feed-forward kind %d is not built for sandwich blocks", l, L.ff_kind);
       B200_CHECK_ARG(m.experts > 0 && m.top > 0 && m.top <= m.experts && m.expert_ff > 0 && m.shared_ff >= 0 && m.router &&
-                         m.w_exp_in && m.w_exp_out && L.ff_norm && L.ff_post_norm && (m.shared_ff == 0 || (L.w_ff_in && L.w_ff_out)),
+                         m.w_exp_in && m.w_exp_out && (L.ff_norm || d.block == B200_BLOCK_POSTNORM) && L.ff_post_norm &&
+                         (m.shared_ff == 0 || (L.w_ff_in && L.w_ff_out)),
                      "engine_create_stack: layer %d: mixture-of-experts description", l);
+      B200_CHECK_ARG((m.router_kind == 0 || m.router_kind == 1) && m.expert_act >= 0 && m.expert_act <= B200_ACT_TANH &&
+                         (m.expert_act == 0 || m.shared_ff == 0 || m.shared_plain),
+                     "engine_create_stack: layer %d: router kind %d / expert activation %d (a plain activation takes a plain shared expert)",
+                     l, m.router_kind, m.expert_act);
       s->any_moe = true;
       s->moe_e_max = std::max(s->moe_e_max, m.experts);
       s->moe_top_max = std::max(s->moe_top_max, m.top);
       s->moe_ff_max = std::max(s->moe_ff_max, m.expert_ff);
-      ff_rows = m.shared_ff > 0 ? up8i(2 * m.shared_ff + 1) : 0;
+      ff_rows = m.shared_ff > 0 ? (m.expert_act != 0 ? up8i(m.shared_ff) : up8i(2 * m.shared_ff + 1)) : 0;
       ff_mid = m.shared_ff;
     }
     s->max_heads = std::max(s->max_heads, a.heads);
@@ -1179,7 +1341,11 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       s->v_slot += (size_t)d.max_ctx * a.kv_heads * a.vdim;
     } else if (RL.mixer == B200_MIX_LATENT) {   // one row per position: [latent | rotated shared key part]
       s->k_slot += (size_t)d.max_ctx * (RL.lat.kv_rank + RL.lat.rot_dim);
-    } else {                                    // no rows per position: a fixed-size state
+    } else if (RL.mixer == B200_MIX_DELTA) {    // no rows per position: a fixed-size state
+      s->s_slot += (size_t)a.heads * a.dim * a.vdim;
+    } else if (RL.mixer == B200_MIX_MAMBA2) {
+      s->s_slot += (size_t)mamba_state_floats(a.heads, a.vdim, RL.mamba.state, RL.mamba.groups, RL.mamba.taps);
+    } else {
       s->s_slot += (size_t)mlstm_state_floats(a.heads, a.dim, a.vdim);
     }
   }
@@ -1213,11 +1379,14 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       s->plans[l].ok_in = s->plans[l].ok_out = s->plans[l].ok_side = false;
       sp.ok_in = plan(&sp.in, L.w_in, L.n_in, d.width, EPI_BIAS_F32);
       sp.ok_out = plan(&sp.out, L.w_out, d.width, L.k_out, EPI_BIAS_F32);
+      if (L.mixer == B200_MIX_DELTA)
+        sp.ok_lora = plan(&sp.lora, L.delta.w2, (int64_t)L.attn.heads * L.attn.dim, up8i(L.delta.rank), EPI_BIAS_F32);
       if (L.ff_kind == B200_FF_DENSE && L.ff > 0) {
         sp.ok_ff_in = plan(&sp.ff_in, L.w_ff_in, L.ff, d.width, EPI_BIAS_F32);
         sp.ok_ff_out = plan(&sp.ff_out, L.w_ff_out, d.width, L.ff, EPI_BIAS_F32);
       } else if (L.ff_kind == B200_FF_MOE && L.moe.shared_ff > 0) {
-        sp.ok_ff_in = plan(&sp.ff_in, L.w_ff_in, up8i(2 * L.moe.shared_ff + 1), d.width, EPI_BIAS_F32);
+        sp.ok_ff_in = plan(&sp.ff_in, L.w_ff_in, L.moe.expert_act != 0 ? up8i(L.moe.shared_ff) : up8i(2 * L.moe.shared_ff + 1),
+                           d.width, EPI_BIAS_F32);
         sp.ok_ff_out = plan(&sp.ff_out, L.w_ff_out, d.width, L.moe.shared_ff, EPI_BIAS_F32);
       }
     }

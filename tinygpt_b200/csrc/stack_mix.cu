@@ -704,6 +704,14 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const MoeRun p) {
   if (t >= p.n_tok) return;
   const int E = p.m.experts, top = p.m.top;
   const float* z = p.z + (int64_t)t * E;
+  // softmax routing: the scores' common denominator (the order of the scores is that of the logits)
+  float zmax = -INFINITY, zsum = 0.f, picked = 0.f;
+  if (p.m.router_kind == 1) {
+    for (int e = lane; e < E; e += 32) zmax = fmaxf(zmax, z[e]);
+    for (int o = 16; o > 0; o >>= 1) zmax = fmaxf(zmax, __shfl_xor_sync(0xffffffffu, zmax, o));
+    for (int e = lane; e < E; e += 32) zsum += expf(z[e] - zmax);
+    zsum = warp_sum(zsum);
+  }
   float last_v = INFINITY;
   int last_i = -1;
   for (int k = 0; k < top; ++k) {
@@ -729,13 +737,17 @@ __global__ void __launch_bounds__(128) moe_route_kernel(const MoeRun p) {
     if (bi == 0x7fffffff) bi = 0;   // fewer finite logits than choices: cannot happen with top <= experts
     if (lane == 0) {
       p.sel_e[(int64_t)t * top + k] = bi;
-      p.sel_w[(int64_t)t * top + k] = 1.f / (1.f + expf(-bv));
+      const float score = p.m.router_kind == 1 ? expf(bv - zmax) / zsum : 1.f / (1.f + expf(-bv));
+      p.sel_w[(int64_t)t * top + k] = score;
+      picked += score;
       if (p.small) p.pair_slot[(int64_t)t * top + k] = t * top + k;   // no sorting: a pair stays where it is
       else atomicAdd(p.plan + bi, 1);
     }
     last_v = bv;
     last_i = bi;
   }
+  if (p.m.router_kind == 1 && lane == 0)   // the chosen scores over their sum, times the design's scale
+    for (int k = 0; k < top; ++k) p.sel_w[(int64_t)t * top + k] = p.sel_w[(int64_t)t * top + k] / (picked + 1e-20f) * p.m.route_scale;
 }
 
 // One CTA: counts → group ends, the row tiles of every group, and a sorted position for every pair.
@@ -770,19 +782,20 @@ __global__ void __launch_bounds__(256) moe_plan_kernel(const MoeRun p) {
   for (int e = threadIdx.x; e < E; e += blockDim.x) counts[e] = 0;   // ready for the next routing
 }
 
-// a_perm[slot of pair, :] = T(score · h[token, :])
+// a_perm[slot of pair, :] = T(score · h[token, :])   (h itself when the weight multiplies the expert's output)
 template <typename T>
 __global__ void __launch_bounds__(128) moe_gather_kernel(const MoeRun p) {
   pdl_trigger();
   pdl_wait();
   const int pair = blockIdx.x, t = pair / p.m.top;
-  const float w = p.sel_w[pair];
+  const float w = p.m.weight_output ? 1.f : p.sel_w[pair];
   const T* src = static_cast<const T*>(p.h) + (int64_t)t * p.width;
   T* dst = static_cast<T*>(p.a_perm) + (int64_t)p.pair_slot[pair] * p.width;
   for (int i = threadIdx.x; i < p.width; i += blockDim.x) dst[i] = cvt<T>(w * ldf<T>(src + i));
 }
 
-// y[t, :] = Σ_k outp[slot of (t, k), :] + sigmoid(sg[t]) · shared[t, :]   — one thread per (token, column)
+// y[t, :] = Σ_k [weight_k ·] outp[slot of (t, k), :] + [sigmoid(sg[t]) ·] shared[t, :]   — one thread per (token, column); the
+// choices are summed in the order they were made, whatever else is in the step
 template <typename T>
 __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeRun p) {
   pdl_trigger();
@@ -793,10 +806,11 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(const MoeRun p) {
   float v = 0.f;
   for (int k = 0; k < top; ++k) {
     const int64_t o = (int64_t)slots[k] * p.width + i;
-    v += p.tc ? __bfloat162float(p.outp_bf[o]) : p.outp[o];
+    const float ov = p.tc ? __bfloat162float(p.outp_bf[o]) : p.outp[o];
+    v = p.m.weight_output ? fmaf(p.sel_w[(int64_t)t * top + k], ov, v) : v + ov;
   }
   if (p.shared != nullptr) {
-    const float gate = 1.f / (1.f + expf(-ldf<T>(static_cast<const T*>(p.sg) + (int64_t)t * p.ld_sg)));
+    const float gate = p.m.shared_plain ? 1.f : 1.f / (1.f + expf(-ldf<T>(static_cast<const T*>(p.sg) + (int64_t)t * p.ld_sg)));
     const int64_t o = (int64_t)t * p.width + i;
     v += gate * (p.shared_f32 ? static_cast<const float*>(p.shared)[o] : ldf<T>(static_cast<const T*>(p.shared) + o));
   }
@@ -1044,7 +1058,14 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(m.experts <= 8192, "moe: more than 8192 experts not built");
   const int P = p.n_tok * m.top, n_tiles = moe_tiles(P, m.experts), E = m.experts, S = p.plan_stride > 0 ? p.plan_stride : E;
   B200_CHECK_ARG(S >= E, "moe: plan stride below the expert count");
+  B200_CHECK_ARG(m.router_kind == 0 || m.router_kind == 1, "moe: router kind %d", m.router_kind);
   int rc;
+  // rows of an expert's in-projection: gate | up of the clamped gated unit, or up alone under a plain activation
+  const int n_up = m.expert_act != 0 ? m.expert_ff : 2 * m.expert_ff;
+  auto hidden = [&]() -> int {
+    if (m.expert_act != 0) return launch_stack_act_mul(p.act, m.expert_ff, p.gu, nullptr, n_up, P, m.expert_ff, m.expert_act, dtype, st);
+    return launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, n_up, P, m.expert_ff, m.limit, dtype, st);
+  };
   if (p.small) {   // a few tokens: router, then every (token, choice) pair is an item of a small product with its expert
     B200_CHECK_ARG(p.n_tok <= kSmallRows, "moe: the small path takes up to %d tokens", kSmallRows);
     SmallGemv rz;
@@ -1055,11 +1076,10 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
     if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_gather_kernel<float>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
     else B200_CUDA(launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
     SmallGemv g;
-    g.a = p.a_perm; g.sa = p.width; g.w = m.w_exp_in; g.sw = 2ll * m.expert_ff * p.width; g.item_mat = p.sel_e;
-    g.c = p.gu; g.sc = 2 * m.expert_ff; g.M = 1; g.N = 2 * m.expert_ff; g.K = p.width; g.items = P;
+    g.a = p.a_perm; g.sa = p.width; g.w = m.w_exp_in; g.sw = (int64_t)n_up * p.width; g.item_mat = p.sel_e;
+    g.c = p.gu; g.sc = n_up; g.M = 1; g.N = n_up; g.K = p.width; g.items = P;
     if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
-    if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, 2 * m.expert_ff, P, m.expert_ff, m.limit, dtype, st)) != B200_OK)
-      return rc;
+    if ((rc = hidden()) != B200_OK) return rc;
     SmallGemv d;
     d.a = p.act; d.sa = m.expert_ff; d.w = m.w_exp_out; d.sw = (int64_t)p.width * m.expert_ff; d.item_mat = p.sel_e;
     d.c = p.outp; d.sc = p.width; d.c_f32 = true; d.M = 1; d.N = p.width; d.K = m.expert_ff; d.items = P;
@@ -1078,7 +1098,7 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
     B200_CUDA(cudaStreamSynchronize(st));
     const __nv_bfloat16* A = (const __nv_bfloat16*)p.a_perm;
     __nv_bfloat16 *GU = (__nv_bfloat16*)p.gu, *ACT = (__nv_bfloat16*)p.act;
-    const int64_t f2 = 2ll * m.expert_ff;
+    const int64_t f2 = n_up;
     // one expert's rows rarely fill the GPU: the experts' products go round eight side streams that fork from and join
     // back into the step's stream
     constexpr int kSide = 8;
@@ -1112,7 +1132,7 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
                                                   p.width, side[n++ % kSide])) != B200_OK)
         return rc;
     if ((rc = join()) != B200_OK) return rc;
-    if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, f2, P, m.expert_ff, m.limit, dtype, st)) != B200_OK) return rc;
+    if ((rc = hidden()) != B200_OK) return rc;
     if ((rc = fork()) != B200_OK) return rc;
     for (int e = 0, row = 0, n = 0; e < E; row = ends[e], ++e)
       if (ends[e] > row && (rc = launch_gemm_bf16(p.outp_bf + (int64_t)row * p.width, ACT + (int64_t)row * m.expert_ff,
@@ -1123,13 +1143,12 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
   } else {
   StackGemm g;
   g.a = p.a_perm; g.lda = p.width; g.k1 = p.width;
-  g.w = m.w_exp_in; g.sw = 2ll * m.expert_ff * p.width;
-  g.M = P; g.N = 2 * m.expert_ff; g.K = p.width;
-  g.epi = SEPI_STORE; g.c = p.gu; g.ldc = 2 * m.expert_ff;
+  g.w = m.w_exp_in; g.sw = (int64_t)n_up * p.width;
+  g.M = P; g.N = n_up; g.K = p.width;
+  g.epi = SEPI_STORE; g.c = p.gu; g.ldc = n_up;
   g.tile_group = p.plan + 2 * S; g.tile_row0 = p.plan + 2 * S + n_tiles; g.group_end = p.plan + S; g.n_tiles = n_tiles;
   if ((rc = launch_stack_gemm(g, dtype, st)) != B200_OK) return rc;
-  if ((rc = launch_stack_glu_clamp(p.act, m.expert_ff, p.gu, 2 * m.expert_ff, P, m.expert_ff, m.limit, dtype, st)) != B200_OK)
-    return rc;
+  if ((rc = hidden()) != B200_OK) return rc;
   StackGemm d;
   d.a = p.act; d.lda = m.expert_ff; d.k1 = m.expert_ff;
   d.w = m.w_exp_out; d.sw = (int64_t)p.width * m.expert_ff;

@@ -231,7 +231,9 @@ __global__ void __launch_bounds__(256) stack_act_mul_kernel(T* __restrict__ y, i
     const int j = (int)(e % n);
     const float gv = ldf<T>(g + r * ld_gu + j);
     const float av = act == B200_ACT_SILU ? silu(gv)
-                     : act == B200_ACT_GELU_ERF ? 0.5f * gv * (1.f + erff(gv * 0.70710678118654752f)) : gelu_tanh(gv);
+                     : act == B200_ACT_GELU_ERF ? 0.5f * gv * (1.f + erff(gv * 0.70710678118654752f))
+                     : act == B200_ACT_RELU2 ? fmaxf(gv, 0.f) * fmaxf(gv, 0.f)
+                     : act == B200_ACT_TANH ? tanhf(gv) : gelu_tanh(gv);
     if (u == nullptr) {   // the activation alone
       y[r * ld_y + j] = cvt<T>(av);
       continue;
@@ -757,8 +759,7 @@ int launch_stack_act_mul(void* y, int64_t ld_y, const void* g, const void* u, in
                          int dtype, cudaStream_t st) {
   STACK_DTYPE_CHECK(dtype);
   B200_CHECK_ARG(y && g && rows > 0 && n > 0, "stack act_mul: bad arguments");
-  B200_CHECK_ARG(act == B200_ACT_GELU_TANH || act == B200_ACT_SILU || act == B200_ACT_GELU_ERF,
-                 "stack act_mul: unknown activation %d", act);
+  B200_CHECK_ARG(act >= B200_ACT_GELU_TANH && act <= B200_ACT_TANH, "stack act_mul: unknown activation %d", act);
   const int64_t total = rows * n;
   if (dtype == B200_F32)
     B200_CUDA(launch_pdl(stack_act_mul_kernel<float>, dim3(grid_cap(total, 256)), dim3(256), 0, st, stack_pdl(), (float*)y, ld_y,

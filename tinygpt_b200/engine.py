@@ -17,8 +17,8 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import models
-from ._lib import (AttnDesc, B200Error, LatentDesc, LayerWeights, MlstmDesc, ModelDesc, MoeDesc, StackDesc, StackLayer,
-                   WeightTable, check, lib, require_device)
+from ._lib import (AttnDesc, AttnPrepDesc, B200Error, DeltaDesc, LatentDesc, LayerWeights, MambaDesc, MlstmDesc, ModelDesc,
+                   MoeDesc, StackDesc, StackLayer, WeightTable, check, lib, require_device)
 
 
 def align_prompts(token_lists, context_size: int, pad_token: int):
@@ -152,12 +152,13 @@ class DecodeEngine:
                 raise B200Error(f"DecodeEngine: {name} must be a contiguous {dt} tensor on {dev}")
             return t.data_ptr()
 
-        acts = {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2}
+        acts = {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2, "relu2": 3, "tanh": 4}
         arr = (StackLayer * len(spec.layers))()
-        sandwich = spec.block == "sandwich"
+        sandwich = spec.block != "parallel"   # a descriptor per sublayer: sandwich and post-norm blocks
         self._rot_tables = {}
+        self._mix_seen = False
         for i, L in enumerate(spec.layers if sandwich else ()):
-            arr[i] = self._sandwich_layer(spec, i, L, ptr, mdt, acts)
+            arr[i] = (self._postnorm_layer if spec.block == "postnorm" else self._sandwich_layer)(spec, i, L, ptr, mdt, acts)
         for i, L in enumerate(() if sandwich else spec.layers):
             a, lay, p = L.attn, spec.layout(i), f"l{i}."
             side = spec.side_dim > 0
@@ -172,7 +173,7 @@ class DecodeEngine:
         runs = spec.runs()
         run_layer = (C.c_int32 * len(runs))(*[r[0] for r in runs])
         run_mix = (C.c_int32 * len(runs))(*[int(r[1]) for r in runs])
-        desc = StackDesc(1 if mdt == torch.float32 else 0, int(sandwich), spec.width, spec.vocab, len(spec.layers), len(runs),
+        desc = StackDesc(1 if mdt == torch.float32 else 0, {"parallel": 0, "sandwich": 1, "postnorm": 2}[spec.block], spec.width, spec.vocab, len(spec.layers), len(runs),
                          run_layer, run_mix, spec.embed_scale, spec.residual_mult, spec.norm_eps, spec.norm_offset,
                          spec.side_dim, spec.side_dim * len(spec.layers), spec.max_ctx, spec.max_slots,
                          ptr("embed", mdt), ptr("mix_in", mdt), ptr("side_table", mdt), ptr("final_norm", torch.float32),
@@ -214,6 +215,53 @@ class DecodeEngine:
                           0, None, None, None, mixer, 2 if L.ff_kind == "moe" else 1, ptr(p + "post_norm", f32),
                           ptr(p + "ff_norm", f32) if has_ff else None, ptr(p + "ff_post_norm", f32) if has_ff else None,
                           ptr(p + "w_ff_in", mdt), ptr(p + "w_ff_out", mdt), lat, rec, moe)
+
+    def _postnorm_layer(self, spec, i, L, ptr, mdt, acts) -> StackLayer:
+        """Descriptor of layer i of a post-norm-block model (prepared attention, generalized delta rule or Mamba-2 mixer;
+        routed feed-forward or none); rotation tables are built here, for the engine's context length."""
+        lay, p = spec.mix_layout(i), f"l{i}."
+        f32 = torch.float32
+        moe, prep, delta, mamba = MoeDesc(), AttnPrepDesc(), DeltaDesc(), MambaDesc()
+        if L.mixer == "attention":
+            a, q = L.attn, L.prep
+            attn = AttnDesc(a.heads, a.kv_heads, a.dim, a.vdim, a.scale, a.window, a.keep_first, int(a.out_gate))
+            tab = None
+            if q.rot is not None:
+                tab = self._rot_tables.get(q.rot)
+                if tab is None:
+                    tab = self._rot_tables[q.rot] = q.rot.table(spec.max_ctx).contiguous().to(self.device)
+            v_mix = 0
+            if q.v_mix:   # the first such layer keeps its values, the later ones mix them in
+                v_mix = 2 if self._mix_seen else 1
+                self._mix_seen = True
+            prep = AttnPrepDesc(int(q.qk_norm), q.rot.dims if q.rot is not None else 0, int(q.v_norm), v_mix,
+                                ptr(p + "q_norm", f32) if q.qk_norm else None, ptr(p + "k_norm", f32) if q.qk_norm else None,
+                                tab.data_ptr() if tab is not None else None, ptr(p + "vmix", f32) if v_mix == 2 else None)
+            mixer = 0
+        elif L.mixer == "general_delta":
+            a = L.delta
+            attn = AttnDesc(a.heads, a.heads, a.dim, a.dim, 1.0, 0, 0, 0)
+            delta = DeltaDesc(a.rank, a.decay_scale, a.unit_eps, ptr(p + "w2", mdt), ptr(p + "w0", f32), ptr(p + "head_norm", f32))
+            mixer = 3
+        elif L.mixer == "mamba2":
+            a = L.mamba
+            attn = AttnDesc(a.heads, a.groups, a.state, a.vdim, 1.0, 0, 0, 0)
+            mamba = MambaDesc(a.state, a.groups, a.conv, a.norm_groups, ptr(p + "conv_w", f32), ptr(p + "conv_b", f32),
+                              ptr(p + "dt_bias", f32), ptr(p + "A_log", f32), ptr(p + "D", f32), ptr(p + "mix_norm", f32))
+            mixer = 4
+        else:
+            raise B200Error(f"DecodeEngine: layer {i}: mixer {L.mixer!r} is not built for post-norm blocks")
+        has_ff = L.ff_kind == "moe" or L.ff > 0
+        if L.ff_kind == "moe":
+            m = L.moe
+            moe = MoeDesc(m.experts, m.top, m.expert_ff, m.shared_ff, m.limit, m.shared_limit, ptr(p + "router", mdt),
+                          ptr(p + "w_exp_in", mdt), ptr(p + "w_exp_out", mdt), {"sigmoid": 0, "softmax": 1}[m.router],
+                          int(m.weight_output), 0 if m.act == "glu_clamp" else acts[m.act], int(m.shared_plain), m.route_scale)
+        return StackLayer(attn, L.ff, acts[L.ff_act], lay.off_q, lay.off_k, lay.off_v, lay.off_g, lay.off_gate, lay.off_up,
+                          lay.n_in, 0, lay.k_out, None, ptr(p + "w_in", mdt), ptr(p + "b_in", f32), ptr(p + "w_out", mdt),
+                          0, None, None, None, mixer, 2 if L.ff_kind == "moe" else 1, ptr(p + "post_norm", f32),
+                          None, ptr(p + "ff_post_norm", f32) if has_ff else None,
+                          ptr(p + "w_ff_in", mdt), ptr(p + "w_ff_out", mdt), LatentDesc(), MlstmDesc(), moe, prep, delta, mamba)
 
     # --------------------------------------------------------------------------------- ragged steps (stack engines)
     def step(self, entries, greedy: bool = False) -> torch.Tensor:

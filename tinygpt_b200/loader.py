@@ -345,8 +345,14 @@ def load_stack_config(model_dir: str | Path, max_ctx: Optional[int] = None,
     arch = doc.get("architecture")
     if arch not in models.ARCHITECTURES:
         raise LoaderError(f"Unsupported architecture: {arch!r} (layer-stack registry: {', '.join(models.ARCHITECTURES)})")
+    shapes = None
+    st = Path(model_dir) / "model.safetensors" if Path(model_dir).is_dir() else None
+    if models.ARCHITECTURES[arch].with_shapes and st is not None and st.exists():
+        f = SafeTensorsFile(st)   # sizes the config leaves to the tensors
+        shapes = {k: tuple(v.get("shape", ())) for k, v in f.header.items() if isinstance(v, dict) and "shape" in v}
+        f.close()
     try:
-        spec = models.ARCHITECTURES[arch](doc)
+        spec = models.ARCHITECTURES[arch](doc, shapes)
     except (KeyError, TypeError, ValueError) as e:
         raise LoaderError(f"config.json: {type(e).__name__}: {e}")
     if max_ctx is not None or max_slots is not None:

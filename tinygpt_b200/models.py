@@ -259,15 +259,93 @@ class MlstmSpec:
 
 @dataclass(frozen=True)
 class MoeSpec:
-    """Sigmoid-routed experts: `top` of `experts` per token, the score multiplies the expert's input; clamped gated experts
-    of width expert_ff (clamp `limit`); shared_ff > 0: a shared expert of that width (clamp shared_limit) behind a
-    per-token sigmoid gate."""
+    """Routed experts: `top` of `experts` per token.  router "sigmoid": the weight is the chosen expert's sigmoid score;
+    "softmax": scores are a softmax over all experts and the chosen ones are divided by their sum (+ 1e-20) and multiplied by
+    route_scale.  The weight multiplies the expert's input, or (weight_output) its output.  act "glu_clamp": clamped gated
+    experts of width expert_ff (clamp `limit`); "relu2": down·relu(up·h)², no gate rows.  shared_ff > 0: a shared expert of
+    that width (clamp shared_limit) behind a per-token sigmoid gate, or (shared_plain) added as it is."""
     experts: int
     top: int
     expert_ff: int
-    limit: float
+    limit: float = 0.0
     shared_ff: int = 0
     shared_limit: float = 0.0
+    router: str = "sigmoid"
+    weight_output: bool = False
+    route_scale: float = 1.0
+    act: str = "glu_clamp"
+    shared_plain: bool = False
+
+
+@dataclass(frozen=True)
+class HalfRotarySpec:
+    """Rotary positions on the first `dims` entries of every head, entry i paired with entry i + dims/2 (rotate-half
+    layout), pair i turned by p·f_i at position p, f_i = base^(-2i/dims).  factor > 0: Llama-3.1 frequency scaling — with
+    the wavelength l = 2π/f, f is kept where l < original/high, divided by factor where l > original/low, and blended
+    linearly in original/l between the two."""
+    dims: int
+    base: float
+    factor: float = 0.0
+    low: float = 0.0
+    high: float = 0.0
+    original: int = 0
+
+    def frequencies(self) -> np.ndarray:
+        i = np.arange(self.dims // 2, dtype=np.float64)
+        f = np.power(float(self.base), -2.0 * i / max(self.dims, 1))
+        if self.factor <= 0:
+            return f
+        wave = 2.0 * np.pi / f
+        blend = (self.original / wave - self.low) / (self.high - self.low)
+        mid = (1.0 - blend) * f / self.factor + blend * f
+        return np.where(wave < self.original / self.high, f, np.where(wave > self.original / self.low, f / self.factor, mid))
+
+    def table(self, max_ctx: int) -> torch.Tensor:
+        """fp32 [max_ctx, dims/2, 2]: {cos, sin}(p·f_i), angles taken in float64."""
+        ang = np.arange(max_ctx, dtype=np.float64)[:, None] * self.frequencies()[None, :]
+        return torch.from_numpy(np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32))
+
+
+@dataclass(frozen=True)
+class AttnPrepSpec:
+    """What happens to q | k | v between the in-projection and the cache: an RMS norm with a weight over the WHOLE query
+    and key projections, rotary positions, every value head divided by its root mean square, and the value mix-in (the
+    first such layer of the model keeps its values, the later ones blend theirs with them by a learned weight)."""
+    qk_norm: bool = False
+    rot: Optional[HalfRotarySpec] = None
+    v_norm: bool = False
+    v_mix: bool = False
+
+
+@dataclass(frozen=True)
+class DeltaSpec:
+    """Generalized delta rule: per head a dim × dim state, per-channel decay exp(−decay_scale·sigmoid(·)) from a low-rank
+    (`rank`) tanh bottleneck, per-channel removal rate along the unit key k / sqrt(Σk² + unit_eps)."""
+    heads: int
+    dim: int
+    rank: int
+    decay_scale: float = math.exp(-0.5)
+    unit_eps: float = 1e-6
+
+
+@dataclass(frozen=True)
+class Mamba2Spec:
+    """Mamba-2: `heads` heads of `vdim` channels, a state of `state` entries per channel, B and C shared by heads/groups
+    heads, a causal convolution of `conv` taps over x | B | C, the gated output RMS-normed in `norm_groups` equal parts."""
+    heads: int
+    vdim: int
+    state: int
+    groups: int
+    conv: int
+    norm_groups: int = 1
+
+    @property
+    def inner(self) -> int:
+        return self.heads * self.vdim
+
+    @property
+    def channels(self) -> int:
+        return self.inner + 2 * self.groups * self.state
 
 
 @dataclass(frozen=True)
@@ -275,17 +353,23 @@ class StackLayerSpec:
     attn: Optional[AttnSpec] = None  # mixer "attention"
     ff: int = 0                      # feed-forward width (gated / dense), 0 = none
     ff_act: str = "gelu_tanh"        # gelu_tanh | silu | gelu_erf
-    mixer: str = "attention"         # attention | latent_attention | mlstm
+    mixer: str = "attention"         # attention | latent_attention | mlstm | general_delta | mamba2
     latent: Optional[LatentSpec] = None
     mlstm: Optional[MlstmSpec] = None
     ff_kind: str = "gated"           # gated | dense | moe
     moe: Optional[MoeSpec] = None
+    prep: Optional[AttnPrepSpec] = None   # attention mixers of sandwich / post-norm blocks
+    delta: Optional[DeltaSpec] = None
+    mamba: Optional[Mamba2Spec] = None
 
 
 @dataclass(frozen=True)
 class MixLayout:
-    """Rows of the merged in-projection of a sandwich block's mixer (segments on multiples of 8, zero padding).
-    latent attention: [q | down];  mLSTM: [q | k | v | out-gate logits | input-gate, forget-gate logits]."""
+    """Rows of the merged in-projection of a sandwich or post-norm block's mixer (segments on multiples of 8, zero padding).
+    latent attention: [q | down];  mLSTM: [q | k | v | out-gate logits | input-gate, forget-gate logits];  attention:
+    [q | k | v];  generalized delta rule: [r | k | v | out-gate logits | removal logits | decay bottleneck] (the last at
+    off_up);  Mamba-2: [z | x | B | C | dt] with z at off_g, x at off_v, B at off_k, C at off_q (x | B | C contiguous), dt at
+    off_gate."""
     off_q: int = 0
     off_k: int = 0
     off_v: int = 0
@@ -293,6 +377,7 @@ class MixLayout:
     off_gate: int = 0
     n_in: int = 0
     k_out: int = 0
+    off_up: int = 0
 
 
 @dataclass(frozen=True)
@@ -332,7 +417,7 @@ class StackSpec:
     max_ctx: int = 4096              # cache rows per slot
     max_slots: int = 8               # sequences the engine holds at a time
     block: str = "parallel"          # parallel: x += m·(mixer(h) + ff(h)), one norm | sandwich: a norm before and after
-    norm_kind: str = "rms"           # each sublayer.  rms | layer (weight-only layer norm)
+    norm_kind: str = "rms"           # each sublayer | postnorm: a norm behind each sublayer only.  rms | layer (weight-only)
     loop_mix: bool = True            # every pass of the loop starts with x <- mix_in·[x; x0]
     logit_softcap: float = 0.0       # > 0: logits <- cap·tanh(logits / cap)
 
@@ -371,6 +456,24 @@ class StackSpec:
             off_g = off_v + _up8(a.heads * a.vdim)
             off_gate = off_g + _up8(a.heads * a.vdim)
             return MixLayout(0, off_k, off_v, off_g, off_gate, off_gate + _up8(2 * a.heads), a.heads * a.vdim)
+        if L.mixer == "attention":
+            a = L.attn
+            off_k = _up8(a.heads * a.dim)
+            off_v = off_k + _up8(a.kv_heads * a.dim)
+            return MixLayout(off_q=0, off_k=off_k, off_v=off_v, n_in=off_v + _up8(a.kv_heads * a.vdim), k_out=a.heads * a.vdim)
+        if L.mixer == "general_delta":
+            a = L.delta
+            seg = _up8(a.heads * a.dim)
+            return MixLayout(off_q=0, off_k=seg, off_v=2 * seg, off_g=3 * seg, off_gate=4 * seg, off_up=5 * seg,
+                             n_in=5 * seg + _up8(a.rank), k_out=a.heads * a.dim)
+        if L.mixer == "mamba2":
+            a = L.mamba
+            off_v = _up8(a.inner)
+            off_k = off_v + a.inner
+            off_q = off_k + a.groups * a.state
+            off_gate = _up8(off_q + a.groups * a.state)
+            return MixLayout(off_q=off_q, off_k=off_k, off_v=off_v, off_g=0, off_gate=off_gate, n_in=off_gate + _up8(a.heads),
+                             k_out=a.inner)
         raise ValueError(f"mix_layout: layer {i} has mixer {L.mixer!r}")
 
     def with_ctx(self, max_ctx: int, max_slots: Optional[int] = None) -> "StackSpec":
@@ -388,11 +491,21 @@ class StackSpec:
             elif L.mixer == "mlstm":
                 q = L.mlstm
                 n += self.width * (2 * q.heads * q.dim + 3 * q.heads * q.vdim + 2 * q.heads)
-            if L.mixer != "attention":
+            elif L.mixer == "general_delta":
+                q = L.delta
+                n += self.width * (6 * q.heads * q.dim + q.rank) + q.heads * q.dim * q.rank
+            elif L.mixer == "mamba2":
+                q = L.mamba
+                n += self.width * (2 * q.inner + 2 * q.groups * q.state + q.heads + q.inner)
+            elif self.block != "parallel":
+                n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + a.heads * a.vdim)
+            if self.block != "parallel":
                 if L.ff_kind == "dense":
                     n += 2 * L.ff * self.width
-                elif L.ff_kind == "moe":   # the router, the chosen experts, the shared expert and its gate
+                elif L.ff_kind == "moe" and L.moe.act == "glu_clamp":   # the router, the chosen experts, the shared expert and its gate
                     n += self.width * (L.moe.experts + 3 * L.moe.top * L.moe.expert_ff + 3 * L.moe.shared_ff + 1)
+                elif L.ff_kind == "moe":
+                    n += self.width * (L.moe.experts + 2 * L.moe.top * L.moe.expert_ff + 2 * L.moe.shared_ff)
                 continue
             n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + (a.heads if a.out_gate else 0) + 2 * L.ff)
             n += self.width * (a.heads * a.vdim + L.ff) + 2 * self.side_dim * self.width
@@ -633,18 +746,246 @@ def pack_silatar_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------- Tekosun
+def tekosun_from_config(doc: dict, name: str = "Tekosun", shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> StackSpec:
+    """config.json of the Tekosun design → StackSpec.  Tekosun: post-norm blocks (x += rms(mixer(x))·w, x += rms(ff(x))·w) with
+    three mixers — a generalized delta rule, Mamba-2, and a sliding-window attention with whole-projection query / key norms,
+    rotate-half rotary positions under Llama-3.1 frequency scaling, unit-rms values and a mix-in of the first such layer's
+    values — and softmax-routed squared-ReLU experts with a plain shared expert; scaled embedding.  `shapes` (tensor name →
+    shape, from the checkpoint's header) gives the one size config.json leaves to the tensors: the rank of the delta rule's
+    decay bottleneck (without it a default stands in, for synthetic checkpoints)."""
+    layers, first_mix = [], True
+    for i, lc in enumerate(doc["layers"]):
+        kind, m = lc.get("type"), lc["mixer"]
+        kw = {}
+        if kind == "attention":
+            rot = None
+            if m.get("rot"):
+                sc = m["rot"].get("scaling") or {}
+                rot = HalfRotarySpec(dims=int(m["rot"]["dims"]), base=float(m["rot"]["base"]), factor=float(sc.get("factor", 0.0)),
+                                     low=float(sc.get("low", 0.0)), high=float(sc.get("high", 0.0)),
+                                     original=int(sc.get("original", 0)))
+                if rot.dims % 2 or rot.dims > int(m["dim"]):
+                    raise ValueError(f"Tekosun: layer {i}: rot.dims {rot.dims} must be even and at most dim")
+                if rot.dims == 0:
+                    rot = None
+            heads, kv = int(m["heads"]), int(m["kv_heads"])
+            if heads % kv:
+                raise ValueError(f"Tekosun: layer {i}: {heads} heads over {kv} kv_heads")
+            kw = dict(mixer="attention",
+                      attn=AttnSpec(heads=heads, kv_heads=kv, dim=int(m["dim"]), vdim=int(m["vdim"]), scale=float(m["scale"]),
+                                    window=int((m.get("mask") or {}).get("size", 0)), keep_first=0, out_gate=False, bias=False),
+                      prep=AttnPrepSpec(qk_norm=True, rot=rot, v_norm=True, v_mix=bool(m.get("v_mix", False))))
+        elif kind == "general_delta":
+            rank = int(shapes[f"l{i}.mix.w1"][0]) if shapes and f"l{i}.mix.w1" in shapes else int(m.get("rank", 16))
+            kw = dict(mixer=kind, delta=DeltaSpec(heads=int(m["heads"]), dim=int(m["dim"]), rank=rank))
+        elif kind == "mamba2":
+            kw = dict(mixer=kind, mamba=Mamba2Spec(heads=int(m["heads"]), vdim=int(m["vdim"]), state=int(m["state"]),
+                                                    groups=int(m["groups"]), conv=int(m["conv"]),
+                                                    norm_groups=int(m.get("norm_groups", 1))))
+            q = kw["mamba"]
+            if q.heads % q.groups or q.inner % q.norm_groups or q.conv < 1:
+                raise ValueError(f"Tekosun: layer {i}: Mamba-2 sizes do not divide")
+        else:
+            raise ValueError(f"Tekosun: layer {i}: mixer type {kind!r} is not part of the design")
+        mlp = lc.get("mlp")
+        if mlp is None:
+            kw.update(ff_kind="dense", ff=0, ff_act="relu2")
+        elif mlp.get("kind") == "moe":
+            sh = mlp.get("shared") or {}
+            kw.update(ff_kind="moe", ff_act="relu2",
+                      moe=MoeSpec(experts=int(mlp["router"]["experts"]), top=int(mlp["router"]["top"]),
+                                  expert_ff=int(mlp["expert"]["ff"]), shared_ff=int(sh.get("ff", 0)), router="softmax",
+                                  weight_output=True, route_scale=float(mlp["router"].get("scale", 1.0)), act="relu2",
+                                  shared_plain=True))
+            if not 1 <= kw["moe"].top <= kw["moe"].experts:
+                raise ValueError(f"Tekosun: layer {i}: top {kw['moe'].top} of {kw['moe'].experts} experts")
+        else:
+            raise ValueError(f"Tekosun: layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of the design")
+        layers.append(StackLayerSpec(**kw))
+    return StackSpec(name=name, architecture="Tekosun", width=int(doc["width"]), vocab=int(doc["vocab"]), layers=tuple(layers),
+                     embed_scale=float((doc.get("embedding") or {}).get("scale", 1.0)), norm_eps=float(doc["norm"]["eps"]),
+                     norm_offset=0.0, block="postnorm", norm_kind="rms", loop_mix=False)
+
+
+def tekosun_config(spec: StackSpec) -> dict:
+    """The config.json a Tekosun StackSpec is read from (inverse of tekosun_from_config; the decay bottleneck's rank
+    travels in the tensors' shapes)."""
+    doc = {"architecture": "Tekosun", "embedding": {"scale": spec.embed_scale}, "layers": [], "norm": {"eps": spec.norm_eps},
+           "vocab": spec.vocab, "width": spec.width}
+    for L in spec.layers:
+        if L.mixer == "attention":
+            a, q = L.attn, L.prep
+            mixer = {"dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "scale": a.scale, "vdim": a.vdim}
+            if a.window > 0:
+                mixer["mask"] = {"size": a.window}
+            if q.rot is not None:
+                mixer["rot"] = {"base": q.rot.base, "dims": q.rot.dims}
+                if q.rot.factor > 0:
+                    mixer["rot"]["scaling"] = {"factor": q.rot.factor, "high": q.rot.high, "low": q.rot.low,
+                                               "original": q.rot.original}
+            if q.v_mix:
+                mixer["v_mix"] = True
+        elif L.mixer == "general_delta":
+            mixer = {"dim": L.delta.dim, "heads": L.delta.heads}
+        else:
+            a = L.mamba
+            mixer = {"conv": a.conv, "groups": a.groups, "heads": a.heads, "norm_groups": a.norm_groups, "state": a.state,
+                     "vdim": a.vdim}
+        mlp = None
+        if L.ff_kind == "moe":
+            mlp = {"expert": {"ff": L.moe.expert_ff}, "kind": "moe",
+                   "router": {"experts": L.moe.experts, "scale": L.moe.route_scale, "top": L.moe.top}}
+            if L.moe.shared_ff > 0:
+                mlp["shared"] = {"ff": L.moe.shared_ff}
+        doc["layers"].append({"mixer": mixer, "mlp": mlp, "type": L.mixer})
+    return doc
+
+
+def tekosun_tensor_shapes(spec: StackSpec) -> Dict[str, Tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a Tekosun model (Linear weights are [out, in])."""
+    W, out = spec.width, {}
+    out["embed"] = (spec.vocab, W)
+    for i, L in enumerate(spec.layers):
+        p = f"l{i}."
+        out[p + "norm1"] = (W,)
+        if L.mixer == "attention":
+            a = L.attn
+            out[p + "mix.q"], out[p + "mix.k"], out[p + "mix.v"] = (a.heads * a.dim, W), (a.kv_heads * a.dim, W), (a.kv_heads * a.vdim, W)
+            out[p + "mix.q.norm"], out[p + "mix.k.norm"] = (a.heads * a.dim,), (a.kv_heads * a.dim,)
+            if L.prep.v_mix:
+                out[p + "mix.vmix"] = ()
+            out[p + "mix.o"] = (W, a.heads * a.vdim)
+        elif L.mixer == "general_delta":
+            a = L.delta
+            n = a.heads * a.dim
+            for nm in ("r", "k", "v", "g", "a"):
+                out[p + "mix." + nm] = (n, W)
+            out[p + "mix.a.b"], out[p + "mix.w0"], out[p + "mix.norm"] = (n,), (n,), (n,)
+            out[p + "mix.w1"], out[p + "mix.w2"] = (a.rank, W), (n, a.rank)
+            out[p + "mix.o"] = (W, n)
+        else:
+            a = L.mamba
+            out[p + "mix.in"] = (2 * a.inner + 2 * a.groups * a.state + a.heads, W)
+            out[p + "mix.conv"], out[p + "mix.conv.b"] = (a.channels, a.conv), (a.channels,)
+            out[p + "mix.dt_bias"], out[p + "mix.A_log"], out[p + "mix.D"] = (a.heads,), (a.heads,), (a.heads,)
+            out[p + "mix.norm"], out[p + "mix.o"] = (a.inner,), (W, a.inner)
+        if L.ff_kind == "moe":
+            out[p + "norm2"] = (W,)
+            for e in range(L.moe.experts):
+                out[f"{p}mlp.e{e}.up"], out[f"{p}mlp.e{e}.down"] = (L.moe.expert_ff, W), (W, L.moe.expert_ff)
+            out[p + "mlp.router"] = (L.moe.experts, W)
+            if L.moe.shared_ff > 0:
+                out[p + "mlp.shared.up"], out[p + "mlp.shared.down"] = (L.moe.shared_ff, W), (W, L.moe.shared_ff)
+    out["final.norm"] = (W,)
+    out["head"] = (spec.vocab, W)
+    return out
+
+
+def synth_tekosun_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic Tekosun checkpoint (bf16, checkpoint names): matrices N(0, std·√(64/in)) (routers four times wider,
+    so that the choice does not hang on the last bit), norm weights 1 + N(0, 0.1), biases N(0, 1), the value mix-in weight
+    in (0.2, 0.6), decays and step sizes in the range where the state both keeps and forgets."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tekosun_tensor_shapes(spec).items():
+        t = torch.randn(shape, generator=g) if len(shape) else torch.randn((), generator=g)
+        if name.endswith("vmix"):
+            t = 0.4 + 0.2 * torch.tanh(t)
+        elif name.endswith("A_log"):
+            t = 0.5 * t
+        elif name.endswith("dt_bias"):
+            t = t - 1.0
+        elif name.endswith("mix.D") or name.endswith("norm") or name.endswith("norm1") or name.endswith("norm2"):
+            t = 1.0 + 0.1 * t
+        elif name.endswith("mix.conv"):
+            t = t * 0.5
+        elif len(shape) == 2:
+            t = t * (std * (64.0 / shape[1]) ** 0.5)
+            if name.endswith("router"):
+                t = t * 4.0
+        w[name] = t.to(torch.bfloat16)
+    return w
+
+
+def pack_tekosun_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="cuda",
+                         dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """Checkpoint tensors (Tekosun names) → the engine's layout on `device`.  Per layer: w_in = the mixer's in-projections
+    merged by rows (StackSpec.mix_layout), b_in fp32 (the delta rule's removal bias), w_out = mix.o; the delta rule's second
+    decay stage with its columns padded to 8; Mamba-2's convolution and per-head vectors in fp32; experts as one
+    [experts, ff, width] and one [experts, width, ff] block; the shared expert's up rows padded to 8.  Vectors in fp32,
+    matrices in `dtype`."""
+    W = spec.width
+    out: Dict[str, torch.Tensor] = {}
+
+    def mat(t):
+        return t.to(dtype).contiguous().to(device)
+
+    def vec(t):
+        return t.to(torch.float32).reshape(-1).contiguous().to(device)
+
+    out["embed"], out["head"], out["final_norm"] = mat(named["embed"]), mat(named["head"]), vec(named["final.norm"])
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.mix_layout(i), f"l{i}."
+        w_in = torch.zeros(lay.n_in, W, dtype=dtype)
+        b_in = torch.zeros(lay.n_in, dtype=torch.float32)
+
+        def put(off, name, bias=None):
+            t = named[p + name]
+            w_in[off:off + t.shape[0]] = t.to(dtype)
+            if bias is not None:
+                b_in[off:off + t.shape[0]] = named[p + bias].to(torch.float32)
+
+        if L.mixer == "attention":
+            put(lay.off_q, "mix.q"), put(lay.off_k, "mix.k"), put(lay.off_v, "mix.v")
+            out[p + "q_norm"], out[p + "k_norm"] = vec(named[p + "mix.q.norm"]), vec(named[p + "mix.k.norm"])
+            if L.prep.v_mix:
+                out[p + "vmix"] = vec(named[p + "mix.vmix"])
+        elif L.mixer == "general_delta":
+            a = L.delta
+            put(lay.off_q, "mix.r"), put(lay.off_k, "mix.k"), put(lay.off_v, "mix.v"), put(lay.off_g, "mix.g")
+            put(lay.off_gate, "mix.a", "mix.a.b"), put(lay.off_up, "mix.w1")
+            w2 = torch.zeros(a.heads * a.dim, _up8(a.rank), dtype=dtype)
+            w2[:, :a.rank] = named[p + "mix.w2"].to(dtype)
+            out[p + "w2"], out[p + "w0"], out[p + "head_norm"] = w2.to(device), vec(named[p + "mix.w0"]), vec(named[p + "mix.norm"])
+        else:
+            a = L.mamba
+            t = named[p + "mix.in"]
+            w_in[lay.off_g:lay.off_g + a.inner] = t[:a.inner].to(dtype)
+            w_in[lay.off_v:lay.off_v + a.channels] = t[a.inner:a.inner + a.channels].to(dtype)
+            w_in[lay.off_gate:lay.off_gate + a.heads] = t[a.inner + a.channels:].to(dtype)
+            out[p + "conv_w"], out[p + "conv_b"] = vec(named[p + "mix.conv"]), vec(named[p + "mix.conv.b"])
+            out[p + "dt_bias"], out[p + "A_log"], out[p + "D"] = vec(named[p + "mix.dt_bias"]), vec(named[p + "mix.A_log"]), vec(named[p + "mix.D"])
+            out[p + "mix_norm"] = vec(named[p + "mix.norm"])
+        out[p + "w_in"], out[p + "b_in"], out[p + "w_out"] = w_in.to(device), b_in.to(device), mat(named[p + "mix.o"])
+        out[p + "post_norm"] = vec(named[p + "norm1"])
+        if L.ff_kind == "moe":
+            m, q = L.moe, p + "mlp."
+            out[p + "ff_post_norm"] = vec(named[p + "norm2"])
+            out[p + "router"] = mat(named[q + "router"])
+            out[p + "w_exp_in"] = mat(torch.stack([named[f"{q}e{e}.up"] for e in range(m.experts)]))
+            out[p + "w_exp_out"] = mat(torch.stack([named[f"{q}e{e}.down"] for e in range(m.experts)]))
+            if m.shared_ff > 0:
+                sh = torch.zeros(_up8(m.shared_ff), W, dtype=dtype)
+                sh[:m.shared_ff] = named[q + "shared.up"].to(dtype)
+                out[p + "w_ff_in"], out[p + "w_ff_out"] = sh.to(device), mat(named[q + "shared.down"])
+    return out
+
+
 @dataclass(frozen=True)
 class Architecture:
     """One design of the layer-stack registry: its config reader and writer, checkpoint tensor list, synthetic checkpoint
-    and the packer into the engine's layout."""
-    from_config: Callable[[dict], StackSpec]
+    and the packer into the engine's layout.  with_shapes: the config reader also takes the checkpoint's tensor shapes
+    (name → shape) for sizes config.json leaves to the tensors."""
+    from_config: Callable[..., StackSpec]
     to_config: Callable[[StackSpec], dict]
     tensor_shapes: Callable[[StackSpec], Dict[str, Tuple[int, ...]]]
     synth_weights: Callable[..., Dict[str, torch.Tensor]]
     pack: Callable[..., Dict[str, torch.Tensor]]
+    with_shapes: bool = False
 
-    def __call__(self, doc: dict) -> StackSpec:
-        return self.from_config(doc)
+    def __call__(self, doc: dict, shapes: Optional[Dict[str, Tuple[int, ...]]] = None) -> StackSpec:
+        return self.from_config(doc, shapes=shapes) if self.with_shapes else self.from_config(doc)
 
 
 # config.json "architecture" → design.  (The Llama-family checkpoints are told apart by "model_type": loader.py.)
@@ -786,6 +1127,8 @@ ARCHITECTURES["Kozusun"] = Architecture(kozusun_from_config, kozusun_config, koz
                                         pack_stack_weights)
 ARCHITECTURES["Silatar"] = Architecture(silatar_from_config, silatar_config, silatar_tensor_shapes, synth_silatar_weights,
                                         pack_silatar_weights)
+ARCHITECTURES["Tekosun"] = Architecture(tekosun_from_config, tekosun_config, tekosun_tensor_shapes, synth_tekosun_weights,
+                                        pack_tekosun_weights, with_shapes=True)
 
 
 # ------------------------------------------------------------------------------------------- checkpoint writer
