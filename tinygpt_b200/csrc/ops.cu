@@ -4,6 +4,8 @@
 #include "common.cuh"
 #include "ops.cuh"
 
+#include <algorithm>
+
 namespace b200 {
 
 // ------------------------------------------------------------------------------------------------------- RMSNorm
@@ -317,10 +319,16 @@ int argmax_chunks(int64_t V) {
   return (int)c;
 }
 
+// The tickets come FIRST, in an area whose size does not follow the row count (up to kArgmaxTicketRows rows): a workspace
+// that serves launches of different row counts keeps row r's ticket at one place, and no launch's partial results ever
+// lie where another launch's ticket (zero at rest, reset by the block that takes the last one) lives.
+constexpr int64_t kArgmaxTicketRows = 1024;
+static inline int64_t argmax_ticket_bytes(int64_t rows) { return ((std::max(rows, kArgmaxTicketRows) * 4 + 15) / 16) * 16; }
+
 int64_t argmax_workspace_bytes(int64_t rows, int64_t V) {
   const int64_t c = argmax_chunks(V);
-  // [rows*c floats][rows*c int64][rows tickets], 16-byte aligned sections
-  return ((rows * c * 4 + 15) / 16) * 16 + rows * c * 8 + ((rows * 4 + 15) / 16) * 16;
+  // [tickets][rows*c floats][rows*c int64], 16-byte aligned sections
+  return argmax_ticket_bytes(rows) + ((rows * c * 4 + 15) / 16) * 16 + rows * c * 8;
 }
 
 int launch_argmax(int64_t* idx, const void* logits, int64_t rows, int64_t V, void* workspace, cudaStream_t st,
@@ -328,9 +336,9 @@ int launch_argmax(int64_t* idx, const void* logits, int64_t rows, int64_t V, voi
   B200_CHECK_ARG(idx && logits && workspace && rows > 0 && V > 0 && rows < 65536, "argmax: bad arguments");
   const int c = argmax_chunks(V);
   uint8_t* ws = (uint8_t*)workspace;
-  float* wv = (float*)ws;
-  int64_t* wi = (int64_t*)(ws + ((rows * c * 4 + 15) / 16) * 16);
-  unsigned int* ticket = (unsigned int*)((uint8_t*)wi + rows * c * 8);
+  unsigned int* ticket = (unsigned int*)ws;
+  float* wv = (float*)(ws + argmax_ticket_bytes(rows));
+  int64_t* wi = (int64_t*)((uint8_t*)wv + ((rows * c * 4 + 15) / 16) * 16);
   B200_CUDA(launch_pdl(argmax_kernel, dim3(c, (unsigned)rows), dim3(256), 0, st, pdl, idx,
                        (const __nv_bfloat16*)logits, V, wv, wi, ticket, pub ? *pub : ArgmaxPublish{}));
   return B200_OK;

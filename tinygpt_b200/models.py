@@ -754,11 +754,15 @@ def tekosun_from_config(doc: dict, name: str = "Tekosun", shapes: Optional[Dict[
     values — and softmax-routed squared-ReLU experts with a plain shared expert; scaled embedding.  `shapes` (tensor name →
     shape, from the checkpoint's header) gives the one size config.json leaves to the tensors: the rank of the delta rule's
     decay bottleneck (without it a default stands in, for synthetic checkpoints)."""
-    layers, first_mix = [], True
+    layers, mix_size = [], None
     for i, lc in enumerate(doc["layers"]):
         kind, m = lc.get("type"), lc["mixer"]
         kw = {}
         if kind == "attention":
+            if m.get("v_mix"):   # the mixed values are those of the same token in another layer: the sizes must agree
+                if mix_size not in (None, (int(m["kv_heads"]), int(m["vdim"]))):
+                    raise ValueError(f"Tekosun: layer {i}: v_mix layers need equal kv_heads and vdim")
+                mix_size = (int(m["kv_heads"]), int(m["vdim"]))
             rot = None
             if m.get("rot"):
                 sc = m["rot"].get("scaling") or {}

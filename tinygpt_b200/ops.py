@@ -236,6 +236,9 @@ def stack_linear(a: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Ten
     return c
 
 
+_ACTS = {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2, "relu2": 3, "tanh": 4}
+
+
 def _attn_desc(heads, kv_heads, dim, vdim, scale, window, keep_first, out_gate):
     from ._lib import AttnDesc
     return AttnDesc(int(heads), int(kv_heads), int(dim), int(vdim), float(scale), int(window), int(keep_first),
@@ -274,7 +277,7 @@ def stack_act_mul(g: torch.Tensor, u: torch.Tensor, act: str = "gelu_tanh") -> t
         raise B200Error("stack_act_mul: g and u must be equally shaped column slices of one row-major matrix")
     y = torch.empty(g.shape, dtype=g.dtype, device=g.device)
     check(lib().b200_stack_act_mul(y.data_ptr(), y.stride(0), g.data_ptr(), u.data_ptr(), g.stride(0), g.shape[0],
-                                   g.shape[1], {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2}[act], _sdt(g), _stream()), "b200_stack_act_mul")
+                                   g.shape[1], _ACTS[act], _sdt(g), _stream()), "b200_stack_act_mul")
     return y
 
 
@@ -282,7 +285,7 @@ def stack_act(g: torch.Tensor, act: str = "gelu_erf") -> torch.Tensor:
     """T( act(g) ) elementwise over a row-major [rows, n]."""
     y = torch.empty(g.shape, dtype=g.dtype, device=g.device)
     check(lib().b200_stack_act_mul(y.data_ptr(), y.stride(0), g.data_ptr(), None, g.stride(0), g.shape[0], g.shape[1],
-                                   {"gelu_tanh": 0, "silu": 1, "gelu_erf": 2}[act], _sdt(g), _stream()), "b200_stack_act_mul")
+                                   _ACTS[act], _sdt(g), _stream()), "b200_stack_act_mul")
     return y
 
 
@@ -365,17 +368,60 @@ def stack_mlstm(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, gates: t
     return out
 
 
-def stack_moe(h: torch.Tensor, router: torch.Tensor, w_exp_in: torch.Tensor, w_exp_out: torch.Tensor, top: int, limit: float):
-    """Routed experts on h [rows, width]: router [E, width], w_exp_in [E, 2·ff, width] (gate | up), w_exp_out [E, width, ff]
-    → (y fp32 [rows, width], chosen int32 [rows, top], scores fp32 [rows, top])."""
+def stack_moe(h: torch.Tensor, router: torch.Tensor, w_exp_in: torch.Tensor, w_exp_out: torch.Tensor, top: int, limit: float = 0.0,
+              *, softmax: bool = False, weight_output: bool = False, act: str = "glu_clamp", route_scale: float = 1.0):
+    """Routed experts on h [rows, width]: router [E, width], w_exp_in [E, 2·ff, width] (gate | up; [E, ff, width] under a plain
+    activation), w_exp_out [E, width, ff] → (y fp32 [rows, width], chosen int32 [rows, top], weights fp32 [rows, top]).
+    softmax: softmax scores with the chosen ones renormalised and scaled (else sigmoid scores); weight_output: the weight
+    multiplies the expert's output (else its input)."""
     import ctypes as C
     from ._lib import MoeDesc
     h = _chk(h, "stack_moe h", h.dtype)
     E, ff2, W = w_exp_in.shape
-    m = MoeDesc(E, int(top), ff2 // 2, 0, float(limit), 0.0, router.data_ptr(), w_exp_in.data_ptr(), w_exp_out.data_ptr())
+    plain = act != "glu_clamp"
+    m = MoeDesc(E, int(top), ff2 if plain else ff2 // 2, 0, float(limit), 0.0, router.data_ptr(), w_exp_in.data_ptr(),
+                w_exp_out.data_ptr(), int(softmax), int(weight_output), _ACTS[act] if plain else 0, 1, float(route_scale))
     y = torch.empty(h.shape[0], W, dtype=torch.float32, device=h.device)
     chosen = torch.empty(h.shape[0], top, dtype=torch.int32, device=h.device)
     scores = torch.empty(h.shape[0], top, dtype=torch.float32, device=h.device)
     check(lib().b200_stack_moe(y.data_ptr(), h.data_ptr(), h.shape[0], W, C.byref(m), chosen.data_ptr(), scores.data_ptr(),
                                _sdt(h), _stream()), "b200_stack_moe")
     return y, chosen, scores
+
+
+# ---- mechanisms of post-norm blocks (csrc/stack_rec.cu)
+def stack_attn_prep(proj: torch.Tensor, off_q: int, off_k: int, off_v: int, pos: torch.Tensor, *, heads, kv_heads, dim, vdim,
+                    eps: float, q_norm: Optional[torch.Tensor] = None, k_norm: Optional[torch.Tensor] = None,
+                    rot_table: Optional[torch.Tensor] = None, v_norm: bool = False, v_mix: int = 0,
+                    vkeep: Optional[torch.Tensor] = None, mix_lambda: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """The preparation of an attention mixer's q | k | v rows, IN PLACE in proj [n_tok, ·] (returned): whole-projection RMS
+    norms with weights (q_norm / k_norm given), rotate-half rotary positions on the first 2·rot_table.shape[1] entries of
+    every head (rot_table fp32 [ctx, dims/2, 2]), unit-rms values, value mix-in (v_mix 1 fills vkeep, 2 blends with it)."""
+    import ctypes as C
+    from ._lib import AttnPrepDesc
+    a = _attn_desc(heads, kv_heads, dim, vdim, 1.0, 0, 0, 0)
+    d = AttnPrepDesc(int(q_norm is not None), 2 * rot_table.shape[1] if rot_table is not None else 0, int(v_norm), int(v_mix),
+                     _ptr(q_norm), _ptr(k_norm), _ptr(rot_table), _ptr(mix_lambda))
+    check(lib().b200_stack_attn_prep(proj.data_ptr(), proj.stride(0), off_q, off_k, off_v, pos.data_ptr(), proj.shape[0],
+                                     C.byref(a), C.byref(d), _ptr(vkeep), vkeep.stride(0) if vkeep is not None else 0, float(eps),
+                                     _sdt(proj), _stream()), "b200_stack_attn_prep")
+    return proj
+
+
+def stack_lin_scan(d: torch.Tensor, b: torch.Tensor, r: torch.Tensor, v: torch.Tensor, state: torch.Tensor, row0: torch.Tensor,
+                   count: torch.Tensor, slot: torch.Tensor, pos: torch.Tensor, *, heads, dk, dv, p: Optional[torch.Tensor] = None,
+                   q: Optional[torch.Tensor] = None, vscale: Optional[torch.Tensor] = None, share: int = 1) -> torch.Tensor:
+    """The linear recurrence S ← diag(d) S − p (qᵀS) + b (v·vscale)ᵀ, o = Sᵀr over the sequences {row0, count} of the operands'
+    rows (all fp32 [rows, ·] with ONE common row stride: column slices of one matrix; slot / pos per row), continuing `state`
+    [slots, heads·dk·dv] → fp32 [rows, heads·dv].  d [rows, heads·dk], or [rows, heads] (one decay per head)."""
+    rows = v.shape[0]
+    ld = v.stride(0)
+    for t in (d, b, r, p, q, vscale):
+        if t is not None and (t.dtype != torch.float32 or t.stride(0) != ld or t.stride(1) != 1):
+            raise B200Error("stack_lin_scan: operands must be fp32 column slices of one row-major matrix")
+    out = torch.zeros(rows, heads * dv, dtype=torch.float32, device=v.device)
+    check(lib().b200_stack_lin_scan(out.data_ptr(), d.data_ptr(), _ptr(p), _ptr(q), b.data_ptr(), r.data_ptr(), v.data_ptr(),
+                                    _ptr(vscale), ld, heads, dk, dv, share, int(d.shape[1] == heads and dk != 1), state.data_ptr(),
+                                    state.stride(0), row0.data_ptr(), count.data_ptr(), slot.data_ptr(), pos.data_ptr(),
+                                    row0.shape[0], rows, _stream()), "b200_stack_lin_scan")
+    return out
