@@ -681,7 +681,16 @@ def main():
                     help="instead of the headline run: prefill / decode throughput of the Silatar layer-stack design (latent "
                          "attention, mLSTM, routed experts) beside the Kozusun design of equal width, vocabulary, layer runs "
                          "and matrix parameters per token (sizes of tinygpt_b200/stack_bench.py, or all)")
+    ap.add_argument("--tekosun-compare", nargs="?", const="all", default=None, metavar="SIZES",
+                    help="instead of the headline run: prefill / decode throughput of the Tekosun layer-stack design (delta rule, "
+                         "Mamba-2, prepared windowed attention, softmax-routed experts) beside the Silatar design of equal width, "
+                         "vocabulary and layer runs (sizes of tinygpt_b200/stack_bench.py, or all)")
     args = ap.parse_args()
+    if args.tekosun_compare is not None:
+        from tinygpt_b200 import build, stack_bench
+        build.build()
+        stack_bench.main_tekosun(args.tekosun_compare, steps=max(1, min(args.steps, 10)), warmup=max(3, args.warmup))
+        return
     if args.silatar_compare is not None:
         from tinygpt_b200 import build, stack_bench
         build.build()

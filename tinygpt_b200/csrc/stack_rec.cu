@@ -102,91 +102,141 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const AttnPrep p) {
 }
 
 // ------------------------------------------------------------------------------------------------------------ the scan
-// One warp per (sequence, head, value column): lane l holds rows l, l + 32, … of its column of S (DR rows per lane); eight
-// columns per CTA.  The CTA walks its sequence CH tokens at a time: the chunk's decay, removal, unit key, key and query
-// rows (fp32, zero past dk) and the eight columns' values sit in shared memory, staged once for all eight warps.  A token
-// costs a warp the removal's dot with the OLD column (one warp sum the update waits for), DR multiply-adds per operand and
-// the output's dot with the NEW column.  Columns never read each other, so the logits of a sequence do not depend on what
-// else is in the step; the order of the sums inside a column is fixed by dk alone.
-template <int DR, bool REMOVE>
+// One warp per (sequence, head, NC value columns): lane l holds rows l, l + 32, … of its columns of S (DR rows per lane and
+// column); 8·NC columns per CTA.  The CTA walks its sequence CH tokens at a time: the chunk's decay, key, query (and removal,
+// unit key) rows (fp32, zero past dk) and the CTA's columns of v sit in shared memory, staged once for all eight warps,
+// while the next chunk's values are already on their way into registers — the walk waits for memory once per sequence.  A
+// token costs a warp the removal's dot with the OLD columns (warp sums the update waits for, NC side by side), DR
+// multiply-adds per operand and column, and the output's dot with the NEW columns.  Columns never read each other, so
+// the result of a sequence does not depend on what else is in the step; the order of the sums inside a column is fixed by
+// dk alone (lane l sums rows l, l + 32, …, then the butterfly), whatever NC is.
+template <int DR, bool REMOVE, int NC>
 __global__ void __launch_bounds__(256) lin_scan_kernel(const LinScan p) {
   pdl_trigger();
   pdl_wait();
   constexpr int DK = 32 * DR;
   constexpr int CH = 2048 / DK >= 32 ? 32 : 2048 / DK;   // tokens per chunk
   constexpr int NV = REMOVE ? 5 : 3;                      // staged vectors per token: d, b, r (, p, q)
+  constexpr int NQ = CH * NV * DK / 256;                  // staged vector elements per thread and chunk
+  constexpr int COLS = 8 * NC;
+  constexpr int NVR = (CH * COLS + 255) / 256;            // staged values per thread and chunk
   __shared__ float s_x[CH][NV][DK];
-  __shared__ float s_v[CH][8];
+  __shared__ float s_v[CH][COLS];
   const int seg = blockIdx.x, hd = blockIdx.y, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, tid = threadIdx.x;
   const int dk = p.dk, dv = p.dv;
-  const int j0 = blockIdx.z * 8, j = j0 + warp;
-  const bool live = j < dv;
+  const int j0 = blockIdx.z * COLS, jw = j0 + warp * NC;
   const int r0 = p.seg_row0 != nullptr ? p.seg_row0[seg] : seg;
   const int cnt = p.seg_count != nullptr ? p.seg_count[seg] : 1;
   float* st = p.state + (int64_t)p.slot[r0] * p.slot_stride + (int64_t)hd * dk * dv;
   const bool fresh = p.pos[r0] == 0;
-  float S[DR];
+  float S[NC][DR];
 #pragma unroll
-  for (int i = 0; i < DR; ++i) {
-    const int d = lane + 32 * i;
-    S[i] = (live && !fresh && d < dk) ? st[(int64_t)d * dv + j] : 0.f;
+  for (int c = 0; c < NC; ++c) {
+#pragma unroll
+    for (int i = 0; i < DR; ++i) {
+      const int d = lane + 32 * i;
+      S[c][i] = (jw + c < dv && !fresh && d < dk) ? st[(int64_t)d * dv + jw + c] : 0.f;
+    }
   }
   const int hs = hd / p.share;   // the head whose b / r vectors this head reads
+  const float* src_d = p.d_scalar ? p.d + hd : p.d + (int64_t)hd * dk;
+  const float* src_b = p.b + (int64_t)hs * dk;
+  const float* src_r = p.r + (int64_t)hs * dk;
+  const float* src_p = REMOVE ? p.p + (int64_t)hd * dk : nullptr;
+  const float* src_q = REMOVE ? p.q + (int64_t)hd * dk : nullptr;
+  float r_x[NQ], r_v[NVR];
+  auto fetch = [&](int c0) {
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) {
+      const int e = tid + 256 * i, t = e / (NV * DK), w = (e / DK) % NV, d = e % DK;
+      float val = 0.f;
+      if (c0 + t < cnt && d < dk) {
+        const int64_t base = (int64_t)(r0 + c0 + t) * p.ld;
+        const float* src = w == 0 ? src_d : w == 1 ? src_b : w == 2 ? src_r : w == 3 ? src_p : src_q;
+        val = src[base + ((w == 0 && p.d_scalar) ? 0 : d)];
+      }
+      r_x[i] = val;
+    }
+#pragma unroll
+    for (int i = 0; i < NVR; ++i) {
+      const int e = tid + 256 * i, t = e / COLS, c = j0 + e % COLS;
+      float val = 0.f;
+      if (e < CH * COLS && c0 + t < cnt && c < dv) {
+        const int64_t base = (int64_t)(r0 + c0 + t) * p.ld;
+        val = p.v[base + (int64_t)hd * dv + c];
+        if (p.vscale != nullptr) val *= p.vscale[base + hd];
+      }
+      r_v[i] = val;
+    }
+  };
+  fetch(0);
   for (int c0 = 0; c0 < cnt; c0 += CH) {
     const int n = min(CH, cnt - c0);
     __syncthreads();   // the previous chunk has been read
-    for (int e = tid; e < n * NV * DK; e += 256) {
-      const int t = e / (NV * DK), w = (e / DK) % NV, d = e % DK;
-      const float* row;
-      float val = 0.f;
-      if (d < dk) {
-        const int64_t base = (int64_t)(r0 + c0 + t) * p.ld;
-        switch (w) {
-          case 0: val = p.d_scalar ? p.d[base + hd] : p.d[base + (int64_t)hd * dk + d]; break;
-          case 1: row = p.b + base + (int64_t)hs * dk; val = row[d]; break;
-          case 2: row = p.r + base + (int64_t)hs * dk; val = row[d]; break;
-          case 3: val = p.p[base + (int64_t)hd * dk + d]; break;
-          default: val = p.q[base + (int64_t)hd * dk + d]; break;
-        }
-      }
-      s_x[t][w][d] = val;
-    }
-    for (int e = tid; e < n * 8; e += 256) {
-      const int t = e / 8, c = j0 + e % 8;
-      const int64_t base = (int64_t)(r0 + c0 + t) * p.ld;
-      float val = c < dv ? p.v[base + (int64_t)hd * dv + c] : 0.f;
-      if (p.vscale != nullptr) val *= p.vscale[base + hd];
-      s_v[t][e % 8] = val;
-    }
+#pragma unroll
+    for (int i = 0; i < NQ; ++i) (&s_x[0][0][0])[tid + 256 * i] = r_x[i];
+#pragma unroll
+    for (int i = 0; i < NVR; ++i)
+      if (tid + 256 * i < CH * COLS) (&s_v[0][0])[tid + 256 * i] = r_v[i];
     __syncthreads();
-    if (!live) continue;
+    if (c0 + CH < cnt) fetch(c0 + CH);
+    if (jw >= dv) continue;   // warps past the last column only help with the staging
     for (int t = 0; t < n; ++t) {
-      const float vj = s_v[t][warp];
-      float rem = 0.f;
+      float rem[NC], dot[NC], vj[NC];
+#pragma unroll
+      for (int c = 0; c < NC; ++c) {
+        rem[c] = dot[c] = 0.f;
+        vj[c] = s_v[t][warp * NC + c];
+      }
       if constexpr (REMOVE) {
 #pragma unroll
-        for (int i = 0; i < DR; ++i) rem = fmaf(s_x[t][4][lane + 32 * i], S[i], rem);
-        rem = warp_sum(rem);
+        for (int i = 0; i < DR; ++i) {
+          const float qq = s_x[t][4][lane + 32 * i];
+#pragma unroll
+          for (int c = 0; c < NC; ++c) rem[c] = fmaf(qq, S[c][i], rem[c]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+          for (int c = 0; c < NC; ++c) rem[c] += __shfl_xor_sync(0xffffffffu, rem[c], o);
+        }
       }
-      float dot = 0.f;
 #pragma unroll
       for (int i = 0; i < DR; ++i) {
         const int d = lane + 32 * i;
-        float sn = s_x[t][0][d] * S[i];
-        if constexpr (REMOVE) sn = fmaf(-s_x[t][3][d], rem, sn);
-        sn = fmaf(s_x[t][1][d], vj, sn);
-        S[i] = sn;
-        dot = fmaf(sn, s_x[t][2][d], dot);
+        const float dd = s_x[t][0][d], bb = s_x[t][1][d], rr = s_x[t][2][d];
+        float pp = 0.f;
+        if constexpr (REMOVE) pp = s_x[t][3][d];
+#pragma unroll
+        for (int c = 0; c < NC; ++c) {
+          float sn = dd * S[c][i];
+          if constexpr (REMOVE) sn = fmaf(-pp, rem[c], sn);
+          sn = fmaf(bb, vj[c], sn);
+          S[c][i] = sn;
+          dot[c] = fmaf(sn, rr, dot[c]);
+        }
       }
-      dot = warp_sum(dot);
-      if (lane == 0) p.o[(int64_t)(r0 + c0 + t) * p.ld_o + (int64_t)hd * dv + j] = dot;
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int c = 0; c < NC; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
+      }
+      if (lane < NC && jw + lane < dv) {
+        float mine = dot[0];
+#pragma unroll
+        for (int c = 1; c < NC; ++c) mine = lane == c ? dot[c] : mine;
+        p.o[(int64_t)(r0 + c0 + t) * p.ld_o + (int64_t)hd * dv + jw + lane] = mine;
+      }
     }
   }
-  if (!live) return;
 #pragma unroll
-  for (int i = 0; i < DR; ++i) {
-    const int d = lane + 32 * i;
-    if (d < dk) st[(int64_t)d * dv + j] = S[i];
+  for (int c = 0; c < NC; ++c) {
+    if (jw + c >= dv) continue;
+#pragma unroll
+    for (int i = 0; i < DR; ++i) {
+      const int d = lane + 32 * i;
+      if (d < dk) st[(int64_t)d * dv + jw + c] = S[c][i];
+    }
   }
 }
 
@@ -242,58 +292,49 @@ __global__ void __launch_bounds__(128) delta_out_kernel(const DeltaRun p) {
 }
 
 // -------------------------------------------------------------------------------------------------------------- Mamba-2
-// One thread per (sequence, channel) walks the sequence's rows in order with the last taps − 1 inputs in registers (from
-// the slot's state, or zeros at position 0): convolution + bias + SiLU into the fp32 workspace, and at the end the slot's
-// new last inputs — the thread is the only reader and writer of its channel's state.  The threads past the channels serve
-// one head each: dt = softplus(logit + bias) and the decay exp(−exp(A_log)·dt) of every row.
+// The rows of a sequence lie side by side in the step, in order: row t − j is position pos[t] − j of the same sequence
+// exactly when it has the same slot and that position.  Inputs from before the step's first row come from the slot's
+// state, which holds the last taps − 1 inputs, oldest first (zeros before position 0).
+__device__ __forceinline__ bool same_seq(const int32_t* slot, const int32_t* pos, int t, int j) {
+  return t - j >= 0 && slot[t - j] == slot[t] && pos[t - j] == pos[t] - j;
+}
+
+// One thread per (row, channel): convolution over the row's own input and the taps − 1 before it + bias + SiLU into the
+// fp32 workspace.  The state is only READ here (mamba_out_kernel, a later launch, moves it on).  The threads past the
+// channels serve one head each: dt = softplus(logit + bias) and the decay exp(−exp(A_log)·dt).
 template <typename T>
 __global__ void __launch_bounds__(128) mamba_conv_kernel(const MambaRun p) {
   pdl_trigger();
   pdl_wait();
-  const int seg = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
+  const int t = blockIdx.x, c = blockIdx.y * 128 + threadIdx.x;
   const int H = p.a.heads, inner = H * p.a.vdim, ch = inner + 2 * p.m.groups * p.m.state, taps = p.m.taps;
-  const int r0 = p.scan.seg_row0 != nullptr ? p.scan.seg_row0[seg] : seg;
-  const int cnt = p.scan.seg_count != nullptr ? p.scan.seg_count[seg] : 1;
   if (c >= ch + H) return;
+  float* f = p.f + (int64_t)t * p.scan.ld;
   if (c >= ch) {
     const int hd = c - ch;
-    const float bias = p.m.dt_bias[hd], rate = expf(p.m.A_log[hd]);
-    for (int t = 0; t < cnt; ++t) {
-      float* f = p.f + (int64_t)(r0 + t) * p.scan.ld;
-      const float dt = softplusf(p.dt[(int64_t)(r0 + t) * p.ld_dt + hd] + bias);
-      f[ch + hd] = expf(-rate * dt);
-      f[ch + H + hd] = dt;
-    }
+    const float dt = softplusf(p.dt[(int64_t)t * p.ld_dt + hd] + p.m.dt_bias[hd]);
+    f[ch + hd] = expf(-expf(p.m.A_log[hd]) * dt);
+    f[ch + H + hd] = dt;
     return;
   }
-  float* cs = p.conv_state + (int64_t)p.scan.slot[r0] * p.scan.slot_stride;
-  const bool fresh = p.scan.pos[r0] == 0;
-  float win[kMambaMaxTaps], w[kMambaMaxTaps];   // win[taps − 1] is the current input
-#pragma unroll
-  for (int j = 0; j < kMambaMaxTaps; ++j) {
-    w[j] = j < taps ? p.m.conv_w[(int64_t)c * taps + j] : 0.f;
-    win[j] = (j < taps - 1 && !fresh) ? cs[(int64_t)j * ch + c] : 0.f;
-  }
-  const float bias = p.m.conv_b[c];
+  const int32_t *slot = p.scan.slot, *pos = p.scan.pos;
   const T* x = static_cast<const T*>(p.proj) + p.off_x + c;
-  for (int t = 0; t < cnt; ++t) {
-    const float cur = ldf<T>(x + (int64_t)(r0 + t) * p.ld_proj);
-    float acc = bias;
-#pragma unroll
-    for (int j = 0; j < kMambaMaxTaps; ++j) {
-      if (j == taps - 1) win[j] = cur;
-      if (j < taps) acc = fmaf(w[j], win[j], acc);
-    }
-    p.f[(int64_t)(r0 + t) * p.scan.ld + c] = siluf(acc);
-#pragma unroll
-    for (int j = 0; j + 1 < kMambaMaxTaps; ++j) win[j] = win[j + 1];
+  const float* cs = p.conv_state + (int64_t)slot[t] * p.scan.slot_stride;
+  float acc = p.m.conv_b[c];
+  int in_step = 0;   // rows of this sequence in front of row t, counted up to taps − 1
+  while (in_step < taps - 1 && same_seq(slot, pos, t, in_step + 1)) ++in_step;
+  for (int j = 0; j < taps; ++j) {   // j positions back; weight column taps − 1 − j
+    float v = 0.f;
+    if (j <= in_step) v = ldf<T>(x + (int64_t)(t - j) * p.ld_proj);
+    else if (pos[t] - j >= 0) v = cs[(int64_t)(taps - 1 - (j - in_step)) * ch + c];   // j − in_step inputs before the step's first row
+    acc = fmaf(p.m.conv_w[(int64_t)c * taps + taps - 1 - j], v, acc);
   }
-#pragma unroll
-  for (int j = 0; j < kMambaMaxTaps; ++j)
-    if (j < taps - 1) cs[(int64_t)j * ch + c] = win[j];
+  f[c] = siluf(acc);
 }
 
-// One CTA per token: y = o + D·x, · silu(z), an RMS norm in norm_groups equal parts, · norm
+// One CTA per token: y = o + D·x, · silu(z), an RMS norm in norm_groups equal parts, · norm.  The CTA of a sequence's LAST row
+// in the step also moves the slot's convolution state on: the last taps − 1 inputs, from the step's rows where it has that
+// many, else from the old state shifted (every thread reads its channel's old entries before it writes any).
 template <typename T>
 __global__ void __launch_bounds__(256) mamba_out_kernel(const MambaRun p) {
   pdl_trigger();
@@ -301,6 +342,33 @@ __global__ void __launch_bounds__(256) mamba_out_kernel(const MambaRun p) {
   __shared__ float red[8];
   const int t = blockIdx.x, tid = threadIdx.x;
   const int H = p.a.heads, dv = p.a.vdim, inner = H * dv, part = inner / p.m.norm_groups;
+  {
+    const int32_t *slot = p.scan.slot, *pos = p.scan.pos;
+    const int taps = p.m.taps, ch = inner + 2 * p.m.groups * p.m.state;
+    const bool last = t + 1 >= p.scan.n_tok || slot[t + 1] != slot[t] || pos[t + 1] != pos[t] + 1;
+    if (last && taps > 1) {
+      int in_step = 0;
+      while (in_step < taps - 1 && same_seq(slot, pos, t, in_step + 1)) ++in_step;
+      float* cs = p.conv_state + (int64_t)slot[t] * p.scan.slot_stride;
+      const T* x = static_cast<const T*>(p.proj) + p.off_x;
+      for (int c = tid; c < ch; c += 256) {
+        float keep[kMambaMaxTaps];
+#pragma unroll
+        for (int i = 0; i < kMambaMaxTaps - 1; ++i) {   // new entry i = the input taps − 2 − i positions back from row t
+          const int j = taps - 2 - i;
+          float v = 0.f;
+          if (i < taps - 1) {
+            if (j <= in_step) v = ldf<T>(x + (int64_t)(t - j) * p.ld_proj + c);
+            else if (pos[t] - j >= 0) v = cs[(int64_t)(taps - 1 - (j - in_step)) * ch + c];
+          }
+          keep[i] = v;
+        }
+#pragma unroll
+        for (int i = 0; i < kMambaMaxTaps - 1; ++i)
+          if (i < taps - 1) cs[(int64_t)i * ch + c] = keep[i];
+      }
+    }
+  }
   const float* o = p.scan.o + (int64_t)t * p.scan.ld_o;
   const float* x = p.f + (int64_t)t * p.scan.ld;
   const T* z = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj + p.off_z;
@@ -339,6 +407,40 @@ __global__ void __launch_bounds__(256) stack_rms_add_cast_kernel(float* __restri
   }
 }
 
+// The same for a few rows that fit the CTA's registers (decode steps, where latency counts): y, w and x are requested
+// together — one memory round trip before the reduction instead of three.  dim <= 16 · 256.
+template <typename YT>
+__global__ void __launch_bounds__(256) stack_rms_add_cast_small_kernel(float* __restrict__ x, const YT* __restrict__ y,
+                                                                       const float* __restrict__ w, __nv_bfloat16* __restrict__ h,
+                                                                       int dim, float eps, float mult) {
+  __shared__ float red[8];
+  pdl_trigger();
+  pdl_wait();
+  const YT* yr = y + (int64_t)blockIdx.x * dim;
+  float* xr = x + (int64_t)blockIdx.x * dim;
+  float yv[16], wv[16], xv[16];
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const int i = threadIdx.x + k * 256;
+    yv[k] = i < dim ? ldf<YT>(yr + i) : 0.f;
+    wv[k] = i < dim ? w[i] : 0.f;
+    xv[k] = i < dim ? xr[i] : 0.f;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < 16; ++k) ss += yv[k] * yv[k];
+  const float inv = 1.f / sqrtf(block_sum(ss, red) / (float)dim + eps);
+#pragma unroll
+  for (int k = 0; k < 16; ++k) {
+    const int i = threadIdx.x + k * 256;
+    if (i < dim) {
+      const float v = xv[k] + mult * (yv[k] * inv * wv[k]);
+      xr[i] = v;
+      if (h != nullptr) h[(int64_t)blockIdx.x * dim + i] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
 }  // namespace
 
 #define REC_DTYPE_CHECK(dtype) \
@@ -363,11 +465,18 @@ int launch_lin_scan(const LinScan& p, cudaStream_t st) {
   B200_CHECK_ARG((p.p == nullptr) == (p.q == nullptr), "linear scan: the removal needs both of its vectors");
   B200_CHECK_ARG(p.heads > 0 && p.dk > 0 && p.dv > 0 && p.share > 0 && p.heads % p.share == 0, "linear scan: bad sizes");
   B200_CHECK_ARG(p.dk <= kScanMaxDim, "linear scan: more than %d key channels not built", kScanMaxDim);
-  const dim3 grid(p.n_seg, p.heads, (p.dv + 7) / 8);
-#define B200_SCAN(DR)                                                                                    \
-  do {                                                                                                   \
-    if (p.p != nullptr) B200_CUDA(launch_pdl(lin_scan_kernel<DR, true>, grid, dim3(256), 0, st, stack_pdl(), p));  \
-    else B200_CUDA(launch_pdl(lin_scan_kernel<DR, false>, grid, dim3(256), 0, st, stack_pdl(), p));     \
+  // two columns per warp where the value size fills them and the registers hold them: half the CTAs stage the same rows
+  const int nc = (p.dv >= 32 && p.dk <= 256) ? 2 : 1;
+  const dim3 grid(p.n_seg, p.heads, (p.dv + 8 * nc - 1) / (8 * nc));
+#define B200_SCAN_NC(DR, NC)                                                                                       \
+  do {                                                                                                             \
+    if (p.p != nullptr) B200_CUDA(launch_pdl(lin_scan_kernel<DR, true, NC>, grid, dim3(256), 0, st, stack_pdl(), p));  \
+    else B200_CUDA(launch_pdl(lin_scan_kernel<DR, false, NC>, grid, dim3(256), 0, st, stack_pdl(), p));           \
+  } while (0)
+#define B200_SCAN(DR)              \
+  do {                             \
+    if (nc == 2) B200_SCAN_NC(DR, 2); \
+    else B200_SCAN_NC(DR, 1);      \
   } while (0)
   if (p.dk <= 32) B200_SCAN(1);
   else if (p.dk <= 64) B200_SCAN(2);
@@ -375,6 +484,7 @@ int launch_lin_scan(const LinScan& p, cudaStream_t st) {
   else if (p.dk <= 256) B200_SCAN(8);
   else B200_SCAN(16);
 #undef B200_SCAN
+#undef B200_SCAN_NC
   return B200_OK;
 }
 
@@ -406,7 +516,7 @@ int run_mamba(const MambaRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(m.groups > 0 && H % m.groups == 0 && m.norm_groups > 0 && inner % m.norm_groups == 0 && N > 0,
                  "mamba2: heads %d, groups %d, norm_groups %d do not divide", H, m.groups, m.norm_groups);
   B200_CHECK_ARG(m.conv_w && m.conv_b && m.dt_bias && m.A_log && m.D && m.norm, "mamba2: null weight");
-  const dim3 cg(p.scan.n_seg, (ch + H + 127) / 128);
+  const dim3 cg(p.scan.n_tok, (ch + H + 127) / 128);
   if (dtype == B200_F32) B200_CUDA(launch_pdl(mamba_conv_kernel<float>, cg, dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(mamba_conv_kernel<__nv_bfloat16>, cg, dim3(128), 0, st, stack_pdl(), p));
   LinScan s = p.scan;
@@ -423,6 +533,15 @@ int run_mamba(const MambaRun& p, int dtype, cudaStream_t st) {
 int launch_stack_rms_add_cast(float* x, const void* y, bool y_bf16, const float* w, __nv_bfloat16* h, int64_t rows, int dim,
                               float eps, float mult, cudaStream_t st) {
   B200_CHECK_ARG(x && y && w && rows > 0 && dim > 0, "stack rms_add_cast: bad arguments");
+  if (rows <= 64 && dim <= 16 * 256) {
+    if (y_bf16)
+      B200_CUDA(launch_pdl(stack_rms_add_cast_small_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x,
+                           (const __nv_bfloat16*)y, w, h, dim, eps, mult));
+    else
+      B200_CUDA(launch_pdl(stack_rms_add_cast_small_kernel<float>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x,
+                           (const float*)y, w, h, dim, eps, mult));
+    return B200_OK;
+  }
   if (y_bf16)
     B200_CUDA(launch_pdl(stack_rms_add_cast_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(256), 0, st, stack_pdl(), x,
                          (const __nv_bfloat16*)y, w, h, dim, eps, mult));

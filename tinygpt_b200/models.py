@@ -760,9 +760,9 @@ def tekosun_from_config(doc: dict, name: str = "Tekosun", shapes: Optional[Dict[
         kw = {}
         if kind == "attention":
             if m.get("v_mix"):   # the mixed values are those of the same token in another layer: the sizes must agree
-                if mix_size not in (None, (int(m["kv_heads"]), int(m["vdim"]))):
-                    raise ValueError(f"Tekosun: layer {i}: v_mix layers need equal kv_heads and vdim")
-                mix_size = (int(m["kv_heads"]), int(m["vdim"]))
+                if mix_size not in (None, int(m["kv_heads"]) * int(m["vdim"])):
+                    raise ValueError(f"Tekosun: layer {i}: v_mix layers need as many value entries per token as the first one")
+                mix_size = int(m["kv_heads"]) * int(m["vdim"])
             rot = None
             if m.get("rot"):
                 sc = m["rot"].get("scaling") or {}

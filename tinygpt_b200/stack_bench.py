@@ -174,6 +174,104 @@ def main_silatar(sizes: str, steps: int, warmup: int) -> None:
     print(json.dumps(compare_silatar(names, steps=steps, warmup=warmup)), flush=True)
 
 
+# Tekosun sizes: six layers [delta rule, attention, Mamba-2, delta rule, attention, Mamba-2], every one with routed experts
+# (32 experts of the Silatar size, top 4, a shared expert).  The model beside it is the Silatar model of the same width,
+# vocabulary and number of layer runs (six): the framework's other design with recurrent mixers, an attention over cached
+# rows and routed experts.
+TEKOSUN_SIZES = {
+    "t2048": dict(width=2048, vocab=65536, heads=16, kv_heads=8, dim=128, window=1024, rot_dims=64, d_heads=16, d_dim=128, rank=64,
+                  m_heads=32, m_vdim=64, m_state=128, m_groups=1, conv=4, experts=32, top=4, expert_ff=1024, shared_ff=1024,
+                  beside="s2048"),
+    "t3072": dict(width=3072, vocab=65536, heads=24, kv_heads=8, dim=128, window=1024, rot_dims=64, d_heads=24, d_dim=128, rank=96,
+                  m_heads=48, m_vdim=64, m_state=128, m_groups=1, conv=4, experts=32, top=4, expert_ff=1536, shared_ff=1536,
+                  beside="s3072"),
+}
+
+
+def tekosun_spec(name: str, max_ctx: int, max_slots: int = 8) -> models.StackSpec:
+    z = TEKOSUN_SIZES[name]
+    rot = models.HalfRotarySpec(dims=z["rot_dims"], base=5e5, factor=8.0, low=1.0, high=4.0, original=2048)
+    attn = models.AttnSpec(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["dim"] ** -0.5, z["window"], 0, out_gate=False, bias=False)
+    prep = models.AttnPrepSpec(qk_norm=True, rot=rot, v_norm=True, v_mix=True)
+    moe = models.MoeSpec(z["experts"], z["top"], z["expert_ff"], shared_ff=z["shared_ff"], router="softmax", weight_output=True,
+                         route_scale=2.0, act="relu2", shared_plain=True)
+    L = models.StackLayerSpec
+    kw = dict(ff_kind="moe", moe=moe, ff_act="relu2")
+    d = L(mixer="general_delta", delta=models.DeltaSpec(z["d_heads"], z["d_dim"], z["rank"]), **kw)
+    a = L(mixer="attention", attn=attn, prep=prep, **kw)
+    m = L(mixer="mamba2", mamba=models.Mamba2Spec(z["m_heads"], z["m_vdim"], z["m_state"], z["m_groups"], z["conv"], 1), **kw)
+    return models.StackSpec(name="tekosun-" + name, architecture="Tekosun", width=z["width"], vocab=z["vocab"],
+                            layers=(d, a, m, d, a, m), embed_scale=8.0, norm_eps=1e-5, block="postnorm", norm_kind="rms",
+                            loop_mix=False, max_ctx=max_ctx, max_slots=max_slots)
+
+
+def device_tekosun_weights(spec: models.StackSpec, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random Tekosun weights straight in the engine's layout on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    W = spec.width
+
+    def mat(*shape):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * (shape[-1] ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, centre=1.0, spread=0.05):
+        return centre + torch.randn(n, generator=g, device=device, dtype=torch.float32) * spread
+
+    w = {"embed": mat(spec.vocab, W), "head": mat(spec.vocab, W), "final_norm": vec(W)}
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.mix_layout(i), f"l{i}."
+        w[p + "post_norm"], w[p + "ff_post_norm"] = vec(W), vec(W)
+        w[p + "w_in"], w[p + "b_in"], w[p + "w_out"] = mat(lay.n_in, W), vec(lay.n_in, 0.0), mat(W, lay.k_out)
+        if L.mixer == "attention":
+            a = L.attn
+            w[p + "q_norm"], w[p + "k_norm"], w[p + "vmix"] = vec(a.heads * a.dim), vec(a.kv_heads * a.dim), vec(1, 0.4)
+        elif L.mixer == "general_delta":
+            a = L.delta
+            w[p + "w2"], w[p + "w0"] = mat(a.heads * a.dim, (a.rank + 7) // 8 * 8), vec(a.heads * a.dim, 0.0, 1.0)
+            w[p + "head_norm"] = vec(a.heads * a.dim)
+        else:
+            a = L.mamba
+            w[p + "conv_w"], w[p + "conv_b"] = vec(a.channels * a.conv, 0.0, 0.4), vec(a.channels, 0.0, 0.2)
+            w[p + "dt_bias"], w[p + "A_log"], w[p + "D"] = vec(a.heads, -1.0, 0.5), vec(a.heads, 0.0, 0.5), vec(a.heads)
+            w[p + "mix_norm"] = vec(a.inner)
+        m = L.moe
+        w[p + "router"] = mat(m.experts, W)
+        w[p + "w_exp_in"], w[p + "w_exp_out"] = mat(m.experts, m.expert_ff, W), mat(m.experts, W, m.expert_ff)
+        w[p + "w_ff_in"], w[p + "w_ff_out"] = mat((m.shared_ff + 7) // 8 * 8, W), mat(W, m.shared_ff)
+    return w
+
+
+def compare_tekosun(sizes: List[str], steps: int = 5, warmup: int = 3, prompt_len: int = 2048, n_decode: int = 32) -> dict:
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    timer = _Timer(dev)
+    max_ctx = prompt_len + n_decode + 8
+    rows = {}
+    for name in sizes:
+        def one(spec, weights):
+            eng = engine.DecodeEngine(spec, weights)
+            k = _measure(eng, True, prompt_len, n_decode, timer, steps, warmup, spec.vocab)
+            k["bytes_per_decode_token"] = eng.bytes_per_token(prompt_len)
+            k["launches_per_decode_token"] = eng.launches_per_token
+            k["matrix_params_per_token"] = spec.weight_params()
+            eng.close()
+            del eng
+            torch.cuda.empty_cache()
+            return k
+        tspec = tekosun_spec(name, max_ctx)
+        k = one(tspec, device_tekosun_weights(tspec, dev))
+        sspec = silatar_spec(TEKOSUN_SIZES[name]["beside"], max_ctx)
+        l = one(sspec, device_silatar_weights(sspec, dev))
+        rows[name] = {"tekosun": k, "silatar": l, "ratio": {m: round(k[m] / l[m], 3) for m in k if m.endswith("tok_s")}}
+    return {"metric": "tekosun_compare", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+            "decode_steps": n_decode, "steps": steps, "warmup": warmup, "l2": "flushed between timed iterations",
+            "sizes": rows}
+
+
+def main_tekosun(sizes: str, steps: int, warmup: int) -> None:
+    names = [s for s in sizes.split(",") if s] if sizes and sizes != "all" else list(TEKOSUN_SIZES)
+    print(json.dumps(compare_tekosun(names, steps=steps, warmup=warmup)), flush=True)
+
+
 class _Timer:
     def __init__(self, device):
         self.device = device
