@@ -111,11 +111,14 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const AttnPrep p) {
 // the result of a sequence does not depend on what else is in the step; the order of the sums inside a column is fixed by
 // dk alone (lane l sums rows l, l + 32, …, then the butterfly), whatever NC is.
 template <int DR, bool REMOVE, int NC>
-__global__ void __launch_bounds__(256) lin_scan_kernel(const LinScan p) {
+__global__ void __launch_bounds__(256, 2) lin_scan_kernel(const LinScan p) {
   pdl_trigger();
   pdl_wait();
   constexpr int DK = 32 * DR;
-  constexpr int CH = 2048 / DK >= 32 ? 32 : 2048 / DK;   // tokens per chunk
+  // tokens per chunk: what 8 KB (with the removal's two extra rows: 4 KB) of one operand hold, 4 … 32 — the next chunk waits
+  // in registers, and two CTAs share an SM
+  constexpr int CH0 = (REMOVE ? 1024 : 2048) / DK;
+  constexpr int CH = CH0 > 32 ? 32 : CH0 < 4 ? 4 : CH0;
   constexpr int NV = REMOVE ? 5 : 3;                      // staged vectors per token: d, b, r (, p, q)
   constexpr int NQ = CH * NV * DK / 256;                  // staged vector elements per thread and chunk
   constexpr int COLS = 8 * NC;
@@ -181,51 +184,66 @@ __global__ void __launch_bounds__(256) lin_scan_kernel(const LinScan p) {
     __syncthreads();
     if (c0 + CH < cnt) fetch(c0 + CH);
     if (jw >= dv) continue;   // warps past the last column only help with the staging
-    for (int t = 0; t < n; ++t) {
-      float rem[NC], dot[NC], vj[NC];
+    for (int t4 = 0; t4 < n; t4 += 4) {   // the outputs' warp sums of four tokens run side by side, off the state's chain
+      float dot[4][NC];
 #pragma unroll
-      for (int c = 0; c < NC; ++c) {
-        rem[c] = dot[c] = 0.f;
-        vj[c] = s_v[t][warp * NC + c];
-      }
-      if constexpr (REMOVE) {
+      for (int u = 0; u < 4; ++u) {
+        const int t = t4 + u;             // t < CH always (CH is a multiple of 4)
 #pragma unroll
-        for (int i = 0; i < DR; ++i) {
-          const float qq = s_x[t][4][lane + 32 * i];
-#pragma unroll
-          for (int c = 0; c < NC; ++c) rem[c] = fmaf(qq, S[c][i], rem[c]);
-        }
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-#pragma unroll
-          for (int c = 0; c < NC; ++c) rem[c] += __shfl_xor_sync(0xffffffffu, rem[c], o);
-        }
-      }
-#pragma unroll
-      for (int i = 0; i < DR; ++i) {
-        const int d = lane + 32 * i;
-        const float dd = s_x[t][0][d], bb = s_x[t][1][d], rr = s_x[t][2][d];
-        float pp = 0.f;
-        if constexpr (REMOVE) pp = s_x[t][3][d];
+        for (int c = 0; c < NC; ++c) dot[u][c] = 0.f;
+        if (t >= n) continue;             // rows past the chunk's end hold zeros: they must not touch the state
+        float rem[NC], vj[NC];
 #pragma unroll
         for (int c = 0; c < NC; ++c) {
-          float sn = dd * S[c][i];
-          if constexpr (REMOVE) sn = fmaf(-pp, rem[c], sn);
-          sn = fmaf(bb, vj[c], sn);
-          S[c][i] = sn;
-          dot[c] = fmaf(sn, rr, dot[c]);
+          rem[c] = 0.f;
+          vj[c] = s_v[t][warp * NC + c];
+        }
+        if constexpr (REMOVE) {
+#pragma unroll
+          for (int i = 0; i < DR; ++i) {
+            const float qq = s_x[t][4][lane + 32 * i];
+#pragma unroll
+            for (int c = 0; c < NC; ++c) rem[c] = fmaf(qq, S[c][i], rem[c]);
+          }
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+            for (int c = 0; c < NC; ++c) rem[c] += __shfl_xor_sync(0xffffffffu, rem[c], o);
+          }
+        }
+#pragma unroll
+        for (int i = 0; i < DR; ++i) {
+          const int d = lane + 32 * i;
+          const float dd = s_x[t][0][d], bb = s_x[t][1][d], rr = s_x[t][2][d];
+          float pp = 0.f;
+          if constexpr (REMOVE) pp = s_x[t][3][d];
+#pragma unroll
+          for (int c = 0; c < NC; ++c) {
+            float sn = dd * S[c][i];
+            if constexpr (REMOVE) sn = fmaf(-pp, rem[c], sn);
+            sn = fmaf(bb, vj[c], sn);
+            S[c][i] = sn;
+            dot[u][c] = fmaf(sn, rr, dot[u][c]);
+          }
         }
       }
 #pragma unroll
       for (int o = 16; o > 0; o >>= 1) {
 #pragma unroll
-        for (int c = 0; c < NC; ++c) dot[c] += __shfl_xor_sync(0xffffffffu, dot[c], o);
-      }
-      if (lane < NC && jw + lane < dv) {
-        float mine = dot[0];
+        for (int u = 0; u < 4; ++u) {
 #pragma unroll
-        for (int c = 1; c < NC; ++c) mine = lane == c ? dot[c] : mine;
-        p.o[(int64_t)(r0 + c0 + t) * p.ld_o + (int64_t)hd * dv + jw + lane] = mine;
+          for (int c = 0; c < NC; ++c) dot[u][c] += __shfl_xor_sync(0xffffffffu, dot[u][c], o);
+        }
+      }
+      if (lane < 4 * NC) {                // lane u·NC + c hands out token t4 + u, column jw + c
+        const int u = lane / NC, c = lane % NC;
+        float mine = 0.f;
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+#pragma unroll
+          for (int cc = 0; cc < NC; ++cc) mine = (uu == u && cc == c) ? dot[uu][cc] : mine;
+        }
+        if (t4 + u < n && jw + c < dv) p.o[(int64_t)(r0 + c0 + t4 + u) * p.ld_o + (int64_t)hd * dv + jw + c] = mine;
       }
     }
   }
@@ -332,9 +350,9 @@ __global__ void __launch_bounds__(128) mamba_conv_kernel(const MambaRun p) {
   f[c] = siluf(acc);
 }
 
-// One CTA per token: y = o + D·x, · silu(z), an RMS norm in norm_groups equal parts, · norm.  The CTA of a sequence's LAST row
-// in the step also moves the slot's convolution state on: the last taps − 1 inputs, from the step's rows where it has that
-// many, else from the old state shifted (every thread reads its channel's old entries before it writes any).
+// First CTA of a token: y = o + D·x, · silu(z), an RMS norm in norm_groups equal parts, · norm.  The other CTAs of a sequence's
+// LAST row in the step move the slot's convolution state on: the last taps − 1 inputs, from the step's rows where it has that
+// many, else from the old state shifted in place.
 template <typename T>
 __global__ void __launch_bounds__(256) mamba_out_kernel(const MambaRun p) {
   pdl_trigger();
@@ -342,7 +360,7 @@ __global__ void __launch_bounds__(256) mamba_out_kernel(const MambaRun p) {
   __shared__ float red[8];
   const int t = blockIdx.x, tid = threadIdx.x;
   const int H = p.a.heads, dv = p.a.vdim, inner = H * dv, part = inner / p.m.norm_groups;
-  {
+  if (blockIdx.y > 0) {   // the CTAs behind the first move the state on, 256 channels each
     const int32_t *slot = p.scan.slot, *pos = p.scan.pos;
     const int taps = p.m.taps, ch = inner + 2 * p.m.groups * p.m.state;
     const bool last = t + 1 >= p.scan.n_tok || slot[t + 1] != slot[t] || pos[t + 1] != pos[t] + 1;
@@ -351,23 +369,19 @@ __global__ void __launch_bounds__(256) mamba_out_kernel(const MambaRun p) {
       while (in_step < taps - 1 && same_seq(slot, pos, t, in_step + 1)) ++in_step;
       float* cs = p.conv_state + (int64_t)slot[t] * p.scan.slot_stride;
       const T* x = static_cast<const T*>(p.proj) + p.off_x;
-      for (int c = tid; c < ch; c += 256) {
-        float keep[kMambaMaxTaps];
-#pragma unroll
-        for (int i = 0; i < kMambaMaxTaps - 1; ++i) {   // new entry i = the input taps − 2 − i positions back from row t
+      for (int c = (blockIdx.y - 1) * 256 + tid; c < ch; c += 256 * (gridDim.y - 1)) {
+        // new entry i = the input taps − 2 − i positions back from row t: a step row, or the old entry i + 1 + in_step — always
+        // further along than anything written so far, so the shift runs in place
+        for (int i = 0; i < taps - 1; ++i) {
           const int j = taps - 2 - i;
           float v = 0.f;
-          if (i < taps - 1) {
-            if (j <= in_step) v = ldf<T>(x + (int64_t)(t - j) * p.ld_proj + c);
-            else if (pos[t] - j >= 0) v = cs[(int64_t)(taps - 1 - (j - in_step)) * ch + c];
-          }
-          keep[i] = v;
+          if (j <= in_step) v = ldf<T>(x + (int64_t)(t - j) * p.ld_proj + c);
+          else if (pos[t] - j >= 0) v = cs[(int64_t)(i + 1 + in_step) * ch + c];
+          cs[(int64_t)i * ch + c] = v;
         }
-#pragma unroll
-        for (int i = 0; i < kMambaMaxTaps - 1; ++i)
-          if (i < taps - 1) cs[(int64_t)i * ch + c] = keep[i];
       }
     }
+    return;
   }
   const float* o = p.scan.o + (int64_t)t * p.scan.ld_o;
   const float* x = p.f + (int64_t)t * p.scan.ld;
@@ -525,8 +539,9 @@ int run_mamba(const MambaRun& p, int dtype, cudaStream_t st) {
   s.p = s.q = nullptr;
   int rc = launch_lin_scan(s, st);
   if (rc != B200_OK) return rc;
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(mamba_out_kernel<float>, dim3(p.scan.n_tok), dim3(256), 0, st, stack_pdl(), p));
-  else B200_CUDA(launch_pdl(mamba_out_kernel<__nv_bfloat16>, dim3(p.scan.n_tok), dim3(256), 0, st, stack_pdl(), p));
+  const dim3 og(p.scan.n_tok, m.taps > 1 ? 1 + std::min((ch + 255) / 256, 16) : 1);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(mamba_out_kernel<float>, og, dim3(256), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(mamba_out_kernel<__nv_bfloat16>, og, dim3(256), 0, st, stack_pdl(), p));
   return B200_OK;
 }
 

@@ -65,7 +65,7 @@ inline int64_t delta_row_floats(int heads, int dim, int vdim) { return (int64_t)
 int run_delta(const DeltaRun& p, int dtype, cudaStream_t st);
 
 // ---- Mamba-2 around the scan
-constexpr int kMambaMaxTaps = 8;
+constexpr int kMambaMaxTaps = 16;
 struct MambaRun {
   b200_attn_desc a{};            // heads, vdim; dim = state
   b200_mamba_desc m{};

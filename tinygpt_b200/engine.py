@@ -258,7 +258,9 @@ class DecodeEngine:
                           ptr(p + "w_exp_in", mdt), ptr(p + "w_exp_out", mdt), {"sigmoid": 0, "softmax": 1}[m.router],
                           int(m.weight_output), 0 if m.act == "glu_clamp" else acts[m.act], int(m.shared_plain), m.route_scale)
         return StackLayer(attn, L.ff, acts[L.ff_act], lay.off_q, lay.off_k, lay.off_v, lay.off_g, lay.off_gate, lay.off_up,
-                          lay.n_in, 0, lay.k_out, None, ptr(p + "w_in", mdt), ptr(p + "b_in", f32), ptr(p + "w_out", mdt),
+                          lay.n_in, 0, lay.k_out, None, ptr(p + "w_in", mdt),
+                          ptr(p + "b_in", f32) if L.mixer == "general_delta" else None,   # the only in-projection with a bias
+                          ptr(p + "w_out", mdt),
                           0, None, None, None, mixer, 2 if L.ff_kind == "moe" else 1, ptr(p + "post_norm", f32),
                           None, ptr(p + "ff_post_norm", f32) if has_ff else None,
                           ptr(p + "w_ff_in", mdt), ptr(p + "w_ff_out", mdt), LatentDesc(), MlstmDesc(), moe, prep, delta, mamba)
