@@ -540,6 +540,22 @@ def test_greedy_generation_through_the_engine(dtype):
             assert g == eng.generate_sync(p, 6).tolist()
 
 
+def test_prompt_longer_than_one_pass_of_the_engine():
+    """A step of more rows than the engine takes through its layers at once goes in several passes: the states, the
+    convolution's last inputs and the caches carry over the seam, also for a batch whose second sequence straddles it."""
+    cfg = config([(delta(heads=2, dim=16), None), (mamba(heads=2, vdim=8, state=8, conv=4), None),
+                  (attn(heads=2, kv_heads=1, dim=8, vdim=8, window=40), moe(experts=4, top=2, ff=16, shared=16))], width=32, vocab=64)
+    n = 4096 + 300
+    eng, w = make(cfg, torch.float32, max_ctx=n + 8, max_slots=2)
+    toks = tokens(n, 64, 3)
+    want = so.forward(cfg, w, toks)
+    idx = list(range(0, n, 211)) + list(range(4090, 4104)) + [n - 1]
+    assert_close(eng.step([(0, toks, idx)]), want[idx], torch.float32, "whole")
+    eng.release(0)
+    got = eng.step([(1, toks[:2500], [2499]), (0, toks[:3000], [0, 2999])])
+    assert_close(got, torch.stack([want[2499], want[0], want[2999]]), torch.float32, "batch over the seam")
+
+
 def test_seek_and_overflow_refused():
     cfg = base_config()
     eng, _ = make(cfg, torch.float32, max_ctx=32)
