@@ -308,7 +308,7 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
   if (n >= g.N) return;
   const int64_t mat = g.item_mat != nullptr ? g.item_mat[z] : z;
   const T* wr = static_cast<const T*>(g.w) + mat * g.sw + (int64_t)n * g.K;
-  const T* a = static_cast<const T*>(g.a) + (int64_t)z * g.sa;
+  const T* a = static_cast<const T*>(g.a) + (int64_t)(z / g.item_div) * g.sa;
   const int M = g.m_total > 0 ? min(g.M, g.m_total - z * g.M) : g.M;
   float acc[kSmallRows];
 #pragma unroll
@@ -898,7 +898,7 @@ int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total,
 
 int launch_small_gemv(const SmallGemv& g, int dtype, cudaStream_t st) {
   MIX_DTYPE_CHECK(dtype);
-  B200_CHECK_ARG(g.a && g.w && g.c && g.M >= 1 && g.M <= kSmallRows && g.N > 0 && g.K > 0 && g.items > 0 && g.items <= 65535,
+  B200_CHECK_ARG(g.a && g.w && g.c && g.M >= 1 && g.M <= kSmallRows && g.N > 0 && g.K > 0 && g.items > 0 && g.items <= 65535 && g.item_div >= 1,
                  "small gemv: bad arguments M=%d N=%d K=%d items=%d", g.M, g.N, g.K, g.items);
   const size_t esz = dtype == B200_F32 ? 4 : 2;
   const size_t al = dtype == B200_F32 ? 32 : 16;   // bytes of one 8-element piece
@@ -1073,10 +1073,15 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
     rz.M = p.n_tok; rz.N = E; rz.K = p.width; rz.items = 1;
     if ((rc = launch_small_gemv(rz, dtype, st)) != B200_OK) return rc;
     B200_CUDA(launch_pdl(moe_route_kernel, dim3((p.n_tok + 3) / 4), dim3(128), 0, st, stack_pdl(), p));
-    if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_gather_kernel<float>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
-    else B200_CUDA(launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
     SmallGemv g;
-    g.a = p.a_perm; g.sa = p.width; g.w = m.w_exp_in; g.sw = (int64_t)n_up * p.width; g.item_mat = p.sel_e;
+    if (m.weight_output) {   // the experts read the token's row itself: no weighted copies to make
+      g.a = p.h; g.sa = p.width; g.item_div = m.top;
+    } else {
+      if (dtype == B200_F32) B200_CUDA(launch_pdl(moe_gather_kernel<float>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+      else B200_CUDA(launch_pdl(moe_gather_kernel<__nv_bfloat16>, dim3(P), dim3(128), 0, st, stack_pdl(), p));
+      g.a = p.a_perm; g.sa = p.width;
+    }
+    g.w = m.w_exp_in; g.sw = (int64_t)n_up * p.width; g.item_mat = p.sel_e;
     g.c = p.gu; g.sc = n_up; g.M = 1; g.N = n_up; g.K = p.width; g.items = P;
     if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
     if ((rc = hidden()) != B200_OK) return rc;

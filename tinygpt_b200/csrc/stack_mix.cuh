@@ -23,13 +23,14 @@ int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu,
 int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total, float cap, cudaStream_t st);
 
 // ---- small products of decode-shaped steps: `items` independent products of up to 8 rows each, one warp per output row.
-// Item z multiplies rows a + m·lda + z·sa (m < M) with matrix w + (item_mat ? item_mat[z] : z)·sw ([N, K] row-major) into
+// Item z multiplies rows a + m·lda + (z / item_div)·sa (m < M) with matrix w + (item_mat ? item_mat[z] : z)·sw ([N, K] row-major) into
 // c + m·ldc + z·sc (T, or fp32 when c_f32).  Serves the per-head folds of latent attention, router and gate logits, and
 // the chosen experts of a few tokens (item = (token, choice) pair, matrix = that pair's expert).
 constexpr int kSmallRows = 8;
 struct SmallGemv {
   const void* a = nullptr;
   int64_t lda = 0, sa = 0;
+  int item_div = 1;              // item z reads rows a + (z / item_div)·sa: item_div consecutive items share their rows
   const void* w = nullptr;
   int64_t sw = 0;
   const int32_t* item_mat = nullptr;
