@@ -342,6 +342,9 @@ __global__ void __launch_bounds__(256) small_gemv_kernel(const SmallGemv g) {
     if (lane == 0) {
       if (g.bias != nullptr) v += g.bias[n];
       if (g.bias_m != nullptr) v += g.bias_m[z * g.M + m];
+      if (g.act == B200_ACT_RELU2) v = fmaxf(v, 0.f) * fmaxf(v, 0.f);
+      else if (g.act == B200_ACT_TANH) v = tanhf(v);
+      else if (g.act == B200_ACT_SILU) v = v / (1.f + expf(-v));
       const int64_t o = (int64_t)m * g.ldc + (int64_t)z * g.sc + (int64_t)n * g.nc;
       if (g.c_f32) static_cast<float*>(g.c)[o] = v;
       else static_cast<T*>(g.c)[o] = cvt<T>(v);
@@ -1082,9 +1085,16 @@ int run_moe(const MoeRun& p, int dtype, cudaStream_t st) {
       g.a = p.a_perm; g.sa = p.width;
     }
     g.w = m.w_exp_in; g.sw = (int64_t)n_up * p.width; g.item_mat = p.sel_e;
-    g.c = p.gu; g.sc = n_up; g.M = 1; g.N = n_up; g.K = p.width; g.items = P;
-    if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
-    if ((rc = hidden()) != B200_OK) return rc;
+    g.M = 1; g.N = n_up; g.K = p.width; g.items = P;
+    const bool act_in_product = m.expert_act == B200_ACT_RELU2 || m.expert_act == B200_ACT_TANH || m.expert_act == B200_ACT_SILU;
+    if (act_in_product) {   // a plain activation rides on the product's store: the hidden rows leave in one launch
+      g.c = p.act; g.sc = m.expert_ff; g.act = m.expert_act;
+      if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
+    } else {
+      g.c = p.gu; g.sc = n_up;
+      if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
+      if ((rc = hidden()) != B200_OK) return rc;
+    }
     SmallGemv d;
     d.a = p.act; d.sa = m.expert_ff; d.w = m.w_exp_out; d.sw = (int64_t)p.width * m.expert_ff; d.item_mat = p.sel_e;
     d.c = p.outp; d.sc = p.width; d.c_f32 = true; d.M = 1; d.N = p.width; d.K = m.expert_ff; d.items = P;

@@ -42,6 +42,7 @@ struct SmallGemv {
   int64_t nc = 1;                // stride of the output row index n inside c
   int m_total = 0;               // > 0: item z has min(M, m_total − z·M) rows (the last item may be short)
   const float* bias_m = nullptr; // [m_total]: bias of row z·M + m
+  int act = -1;                  // B200_ACT_RELU2 / _TANH / _SILU: applied to the fp32 sum (+ bias) before it is stored
 };
 int launch_small_gemv(const SmallGemv& g, int dtype, cudaStream_t st);
 // C[rows, n] (fp32) = A[rows, K]·W[n, K]ᵀ + bias[n] for a FEW output columns n and any number of rows (router and gate
