@@ -252,7 +252,7 @@ def _scan_run(cols, kw, H, dk, dv, steps, slot, state):
 
 
 @pytest.mark.parametrize("form", ["delta", "ssm"])
-@pytest.mark.parametrize("sizes", [(3, 16, 24), (1, 40, 7), (2, 33, 64), (4, 8, 9), (2, 130, 5)])
+@pytest.mark.parametrize("sizes", [(3, 16, 24), (1, 40, 7), (2, 33, 64), (4, 8, 9), (2, 130, 5), (1, 200, 40), (1, 300, 33)])
 def test_linear_recurrence_scan_op_and_carried_state(form, sizes):
     H, dk, dv = sizes
     n = 70
