@@ -35,7 +35,7 @@ extern "C" {
  * blocks, latent attention, mLSTM, routed experts;  6: + post-norm blocks, the prepared attention (b200_attn_prep_desc), the
  * generalized delta rule, Mamba-2, softmax-routed experts (fields appended to b200_moe_desc and b200_stack_layer),
  * b200_stack_lin_scan, b200_stack_attn_prep.  All additive: callers of an older version keep working. */
-#define B200_ABI_VERSION 6
+#define B200_ABI_VERSION 7
 
 typedef enum b200_status {
   B200_OK = 0,
@@ -309,9 +309,12 @@ typedef enum b200_norm_kind { B200_NORM_RMS = 0, B200_NORM_LAYER = 1 } b200_norm
  * head with a per-channel decay and a rank-one removal along the unit key (b200_delta_desc).  MAMBA2: a short causal
  * convolution and a scalar-decay state-space recurrence per head (b200_mamba_desc); the convolution's last inputs are part
  * of the state.  In sandwich and post-norm blocks ATTENTION is the windowed attention of b200_attn_desc behind the
- * per-token preparation of b200_attn_prep_desc (query / key norms, rotary positions, value norm, value mix-in). */
+ * per-token preparation of b200_attn_prep_desc (query / key norms, rotary positions, value norm, value mix-in).
+ * GATED_DELTA: the gated delta rule — a key × value matrix per head with one decay per head and a removal along the unit
+ * key weighted by a per-head write strength, behind short causal convolutions (b200_gdelta_desc). */
 typedef enum b200_mixer_kind {
-  B200_MIX_ATTENTION = 0, B200_MIX_LATENT = 1, B200_MIX_MLSTM = 2, B200_MIX_DELTA = 3, B200_MIX_MAMBA2 = 4
+  B200_MIX_ATTENTION = 0, B200_MIX_LATENT = 1, B200_MIX_MLSTM = 2, B200_MIX_DELTA = 3, B200_MIX_MAMBA2 = 4,
+  B200_MIX_GATED_DELTA = 5
 } b200_mixer_kind;
 /* GATED: act(gate)·up → down (merged into w_in / w_out).  DENSE: act(up) → down.  MOE: routed clamped gated experts
  * (+ optional gated shared expert), b200_moe_desc. */
@@ -326,9 +329,10 @@ typedef struct b200_attn_desc {
   int32_t window;      /* key j visible from query i when j <= i and i - j < window; 0 = every earlier key */
   int32_t keep_first;  /* keys j < keep_first stay visible whatever the window */
   int32_t out_gate;    /* 1: head output × sigmoid(gate logit of that head) */
+  int32_t sink;        /* 1: the softmax's denominator gains 1 — a sink of score 0 that has no value */
 } b200_attn_desc;
 
-/* Latent attention (sizes heads / dim / vdim / scale in b200_attn_desc; kv_heads = 1, no window, no gate).  Per head the
+/* Latent attention (sizes heads / dim / vdim / scale / window in b200_attn_desc; kv_heads = 1, no per-head gate).  Per head the
  * query is [dim plain | rot_dim rotated]; w_in rows are [q: heads·(dim + rot_dim) | down: kv_rank + rot_dim] (the down
  * segment starts at off_k).  c = rms(down[:kv_rank])·c_norm is the latent, down[kv_rank:] rotated is the key part all
  * heads share; the slot's cache row of a position is [c | rotated key part].  score = (q_plain·(uk_h c) + q_rot·k_rot)·scale,
@@ -341,6 +345,13 @@ typedef struct b200_latent_desc {
   const void* uk;           /* [heads·dim][kv_rank] as stored, or NULL (then prompts take the general kernels) */
   const void* uv;           /* [heads·vdim][kv_rank] */
   const float* rot_table;   /* [max_ctx][rot_dims/2][2] fp32 */
+  /* variants (all 0 / NULL: the form above) */
+  int32_t rot_half;         /* 1: entry i of the rotated part is paired with entry i + rot_dims/2 instead of (2i, 2i+1) */
+  int32_t q_rank;           /* > 0: queries go through a latent — w_in's q segment holds q_rank rows (the down-projection),
+                             * q = uq·(rms(those rows)·q_norm) */
+  const float* q_norm;      /* [q_rank] */
+  const void* uq;           /* [heads·(dim + rot_dim)][q_rank] */
+  int32_t out_gate;         /* 1: the concatenated head outputs × sigmoid(gate logits), heads·vdim rows of w_in at off_g */
 } b200_latent_desc;
 
 /* mLSTM (sizes heads / dim / vdim in b200_attn_desc).  w_in rows [q | k | v | out gate: heads·vdim | gates: 2·heads] at
@@ -386,6 +397,7 @@ typedef struct b200_attn_prep_desc {
   const float* k_norm;      /* [kv_heads·dim] */
   const float* rot_table;   /* [max_ctx][rot_dims/2][2] fp32 */
   const float* mix_lambda;  /* [1] */
+  int32_t rot_interleaved;  /* 1: pair i is entries (2i, 2i+1) of the head instead of (i, i + rot_dims/2) */
 } b200_attn_prep_desc;
 
 /* Generalized delta rule (sizes heads / dim / vdim in b200_attn_desc).  w_in rows [r | k | v | out gate: heads·vdim |
@@ -415,6 +427,23 @@ typedef struct b200_mamba_desc {
   const float* D;           /* [heads] */
   const float* norm;        /* [inner] */
 } b200_mamba_desc;
+
+/* Gated delta rule (heads = value heads, kv_heads = query / key heads, dim, vdim in b200_attn_desc; value head h reads
+ * query / key head h / (heads / kv_heads)).  w_in rows [q: kv_heads·dim | k: kv_heads·dim | v: heads·vdim | out gate:
+ * heads·vdim | write strength: heads | decay logit: heads] at off_q / off_k / off_v / off_g / off_gate / off_up.  q, k and v
+ * pass a causal convolution of `taps` taps per channel (conv_w [channels, taps] over q | k | v, last column the current
+ * token's, no bias; zeros before the sequence) and SiLU; q and k become unit vectors per head, x / sqrt(Σx² + unit_eps), q
+ * also times dim^(−1/2).  beta = sigmoid(strength), g = exp(−exp(A_log)·softplus(decay logit + dt_bias)).  Per head:
+ * S <- g·S;  u = beta·(v − Sᵀk);  S <- S + k uᵀ;  o = Sᵀq.  Then o / rms(o) · head_norm · silu(out gate).  The state S (fp32)
+ * and the convolutions' last taps − 1 inputs live in the slot. */
+typedef struct b200_gdelta_desc {
+  int32_t taps;
+  float unit_eps;
+  const float* conv_w;      /* [2·kv_heads·dim + heads·vdim, taps] */
+  const float* A_log;       /* [heads] */
+  const float* dt_bias;     /* [heads] */
+  const float* head_norm;   /* [vdim], shared by the heads */
+} b200_gdelta_desc;
 
 typedef struct b200_stack_layer {
   b200_attn_desc attn;
@@ -447,6 +476,11 @@ typedef struct b200_stack_layer {
   b200_attn_prep_desc prep;
   b200_delta_desc delta;
   b200_mamba_desc mamba;
+  b200_gdelta_desc gdelta;
+  const float* b_out;    /* [width] bias of the mixer's out-projection, or NULL */
+  int32_t kv_share;      /* attention mixers: > 0: this layer has no key / value rows in w_in and no cache of its own — it
+                          * reads the rows that layer kv_share − 1 (an earlier attention layer with equal kv_heads, dim and
+                          * vdim) cached for the same positions */
 } b200_stack_layer;
 
 typedef struct b200_stack_desc {

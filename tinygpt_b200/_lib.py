@@ -37,13 +37,15 @@ class WeightTable(C.Structure):
 
 class AttnDesc(C.Structure):
     _fields_ = [("heads", C.c_int32), ("kv_heads", C.c_int32), ("dim", C.c_int32), ("vdim", C.c_int32),
-                ("scale", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("out_gate", C.c_int32)]
+                ("scale", C.c_float), ("window", C.c_int32), ("keep_first", C.c_int32), ("out_gate", C.c_int32),
+                ("sink", C.c_int32)]
 
 
 class LatentDesc(C.Structure):
     _fields_ = [("kv_rank", C.c_int32), ("rot_dim", C.c_int32), ("rot_dims", C.c_int32),
                 ("c_norm", C.c_void_p), ("uk_t", C.c_void_p), ("uk", C.c_void_p), ("uv", C.c_void_p),
-                ("rot_table", C.c_void_p)]
+                ("rot_table", C.c_void_p), ("rot_half", C.c_int32), ("q_rank", C.c_int32), ("q_norm", C.c_void_p),
+                ("uq", C.c_void_p), ("out_gate", C.c_int32)]
 
 
 class MlstmDesc(C.Structure):
@@ -60,7 +62,8 @@ class MoeDesc(C.Structure):
 
 class AttnPrepDesc(C.Structure):
     _fields_ = [("qk_norm", C.c_int32), ("rot_dims", C.c_int32), ("v_norm", C.c_int32), ("v_mix", C.c_int32),
-                ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("rot_table", C.c_void_p), ("mix_lambda", C.c_void_p)]
+                ("q_norm", C.c_void_p), ("k_norm", C.c_void_p), ("rot_table", C.c_void_p), ("mix_lambda", C.c_void_p),
+                ("rot_interleaved", C.c_int32)]
 
 
 class DeltaDesc(C.Structure):
@@ -74,6 +77,11 @@ class MambaDesc(C.Structure):
                 ("D", C.c_void_p), ("norm", C.c_void_p)]
 
 
+class GatedDeltaDesc(C.Structure):
+    _fields_ = [("taps", C.c_int32), ("unit_eps", C.c_float), ("conv_w", C.c_void_p), ("A_log", C.c_void_p),
+                ("dt_bias", C.c_void_p), ("head_norm", C.c_void_p)]
+
+
 class StackLayer(C.Structure):
     _fields_ = [("attn", AttnDesc), ("ff", C.c_int32), ("ff_act", C.c_int32),
                 ("off_q", C.c_int32), ("off_k", C.c_int32), ("off_v", C.c_int32), ("off_g", C.c_int32),
@@ -85,7 +93,8 @@ class StackLayer(C.Structure):
                 ("post_norm", C.c_void_p), ("ff_norm", C.c_void_p), ("ff_post_norm", C.c_void_p),
                 ("w_ff_in", C.c_void_p), ("w_ff_out", C.c_void_p),
                 ("lat", LatentDesc), ("rec", MlstmDesc), ("moe", MoeDesc),
-                ("prep", AttnPrepDesc), ("delta", DeltaDesc), ("mamba", MambaDesc)]
+                ("prep", AttnPrepDesc), ("delta", DeltaDesc), ("mamba", MambaDesc), ("gdelta", GatedDeltaDesc),
+                ("b_out", C.c_void_p), ("kv_share", C.c_int32)]
 
 
 class StackDesc(C.Structure):

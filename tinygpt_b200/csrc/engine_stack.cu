@@ -32,6 +32,10 @@
 // with three more mixers: the windowed attention behind a per-token preparation of q | k | v (norms, rotary positions,
 // value mix-in), the generalized delta rule and Mamba-2 — two recurrences that share one scan kernel and keep their fp32
 // state (and the convolution's last inputs) in the slot, beside the caches of the attention runs.
+//
+// Sandwich blocks also take the prepared attention (biases, either rotary layout, a sink in the softmax; a layer may read the
+// keys and values an earlier layer cached instead of projecting its own), the latent attention with a query latent, a
+// sliding window and an element-wise output gate, and the gated delta rule behind short convolutions.
 #include <algorithm>
 #include <cstring>
 #include <map>
@@ -56,7 +60,9 @@ struct StackEngine {
   // caches: [slot][run][max_ctx][kv_heads·dim] and [slot][run][max_ctx][kv_heads·vdim]
   uint8_t* cache = nullptr;
   uint8_t *kbase = nullptr, *vbase = nullptr;
-  std::vector<size_t> run_k_off, run_v_off;   // elements from the start of a slot
+  std::vector<size_t> run_k_off, run_v_off;   // elements from the start of a slot (a run that shares another run's keys and
+                                              // values carries that run's offsets)
+  std::vector<char> run_kv_shared;            // the run reads another run's cache and writes none
   size_t k_slot = 0, v_slot = 0;              // elements per slot
   // per-slot device state
   uint8_t* state = nullptr;
@@ -128,9 +134,11 @@ struct StackEngine {
   float *rec_f = nullptr, *rec_wl = nullptr;
   void *rec_lr = nullptr, *vkeep = nullptr;
   int rec_f_max = 0, rec_wl_max = 0, rec_lr_max = 0, vkeep_max = 0;
+  void* latq = nullptr;            // [tok, heads·(dim + rot_dim)] T: queries that came through a latent of their own
+  int latq_max = 0;
   struct SPlans {
-    GemvPlan in{}, out{}, ff_in{}, ff_out{}, lora{};
-    bool ok_in = false, ok_out = false, ok_ff_in = false, ok_ff_out = false, ok_lora = false;
+    GemvPlan in{}, out{}, ff_in{}, ff_out{}, lora{}, uq{};
+    bool ok_in = false, ok_out = false, ok_ff_in = false, ok_ff_out = false, ok_lora = false, ok_uq = false;
   };
   std::vector<SPlans> splans;
 };
@@ -229,6 +237,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   const size_t o_lq = take(lx ? T * s->lat_hd_max * 2 : 0);
   const size_t o_rf = take(T * s->rec_f_max * 4), o_rw = take(T * s->rec_wl_max * 4);
   const size_t o_rl = take(T * s->rec_lr_max * s->esz), o_vk = take(T * s->vkeep_max * s->esz);
+  const size_t o_lqq = take(T * s->latq_max * s->esz);
   B200_CUDA(cudaMalloc((void**)&s->ws, off));
   B200_CUDA(cudaMemset(s->ws, 0, off));
   s->lat_c = lx ? (__nv_bfloat16*)(s->ws + o_lc) : nullptr;
@@ -240,6 +249,7 @@ static int stack_workspace(StackEngine* s, int tok, int rows) {
   s->rec_wl = (float*)(s->ws + o_rw);
   s->rec_lr = s->ws + o_rl;
   s->vkeep = s->ws + o_vk;
+  s->latq = s->ws + o_lqq;
   s->ws_tok = tok;
   s->ws_rows = rows;
   s->x = (float*)(s->ws + o_x);
@@ -442,7 +452,7 @@ static int stack_attention(StackEngine* s, const StackAttn& a, const b200_stack_
                                          d.out_gate ? prow + a.off_g : nullptr, a.ld_proj,
                                          (const __nv_bfloat16*)a.kcache + (size_t)g.slot * a.k_slot_stride,
                                          (const __nv_bfloat16*)a.vcache + (size_t)g.slot * a.v_slot_stride, g.count, d.heads,
-                                         d.kv_heads, d.dim, g.pos0, d.scale, d.window, d.keep_first, st)) != B200_OK)
+                                         d.kv_heads, d.dim, g.pos0, d.scale, d.window, d.keep_first, st, d.sink)) != B200_OK)
       return rc;
   }
   return B200_OK;
@@ -552,14 +562,15 @@ static int stack_norm_add_next(StackEngine* s, float* x, const void* y, bool y_b
 }
 
 static int stack_lin_norm_add(StackEngine* s, const void* A, const void* Wt, int M, int K, const GemvPlan* plan,
-                              const float* norm_w, float* x, const float* next_w, cudaStream_t st) {
+                              const float* norm_w, float* x, const float* next_w, cudaStream_t st, const float* bias = nullptr) {
   const int W = s->d.width;
   int rc;
   if (s->fast && !(M <= kMaxBatch && plan != nullptr) && M >= kGemmRows && gemm_shape_ok(W, K)) {
     if ((rc = launch_gemm_bf16(s->lin_tmp, A, Wt, M, W, K, st)) != B200_OK) return rc;
+    if (bias && (rc = launch_stack_bias_add((__nv_bfloat16*)s->lin_tmp, bias, M, W, st)) != B200_OK) return rc;
     return stack_norm_add_next(s, x, s->lin_tmp, true, norm_w, next_w, M, st);
   }
-  if ((rc = stack_lin(s, A, Wt, nullptr, M, W, K, plan, nullptr, s->y, st)) != B200_OK) return rc;
+  if ((rc = stack_lin(s, A, Wt, bias, M, W, K, plan, nullptr, s->y, st)) != B200_OK) return rc;
   return stack_norm_add_next(s, x, s->y, false, norm_w, next_w, M, st);
 }
 
@@ -619,11 +630,13 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     seq.n_seg = (int)s->segs.size(); seq.seg_row0 = s->m_seg_row0; seq.seg_count = s->m_seg_count;
   }
   if (L.mixer == B200_MIX_ATTENTION) {
+    const bool shared_kv = s->run_kv_shared[r] != 0;   // the keys and values of these positions are in another run's cache already
     if (L.prep.qk_norm || L.prep.rot_dims > 0 || L.prep.v_norm || L.prep.v_mix) {
       AttnPrep ap;
       ap.a = L.attn; ap.d = L.prep; ap.eps = d.norm_eps;
       ap.proj = s->proj; ap.ld_proj = L.n_in; ap.off_q = L.off_q; ap.off_k = L.off_k; ap.off_v = L.off_v;
       ap.pos = s->m_pos; ap.n_tok = n_tok; ap.vkeep = s->vkeep; ap.ld_keep = s->vkeep_max;
+      ap.q_only = shared_kv ? 1 : 0;
       if ((rc = launch_attn_prep(ap, dt, st)) != B200_OK) return rc;
     }
     StackAttn a;
@@ -637,9 +650,23 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     a.out = s->mid; a.ld_out = L.k_out;
     bool single = true;   // decode steps append K/V inside the attention launch
     for (const StackEngine::Seg& g : s->segs) single = single && g.count == 1;
-    a.own_from_proj = single ? 1 : 0;
-    if (!a.own_from_proj && (rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
+    a.own_from_proj = single && !shared_kv ? 1 : 0;
+    if (!a.own_from_proj && !shared_kv && (rc = launch_stack_kv_store(a, dt, st)) != B200_OK) return rc;
     if ((rc = stack_attention(s, a, L, st)) != B200_OK) return rc;
+  } else if (L.mixer == B200_MIX_GATED_DELTA) {
+    const int H = L.attn.heads, G = L.attn.kv_heads;
+    GatedDeltaRun m;
+    m.a = L.attn; m.d = L.gdelta; m.eps = d.norm_eps;
+    m.proj = s->proj; m.ld_proj = L.n_in;
+    m.off_q = L.off_q; m.off_k = L.off_k; m.off_v = L.off_v; m.off_g = L.off_g; m.off_b = L.off_gate; m.off_a = L.off_up;
+    m.f = s->rec_f;
+    m.scan = seq;
+    m.scan.ld = gdelta_row_floats(H, G, L.attn.dim, L.attn.vdim);
+    m.scan.state = s->rstate + s->run_s_off[r]; m.scan.slot_stride = (int64_t)s->s_slot;
+    m.conv_state = m.scan.state + (size_t)H * L.attn.dim * L.attn.vdim;
+    m.scan.o = s->rec_o; m.scan.ld_o = (int64_t)H * L.attn.vdim;
+    m.mid = s->mid; m.ld_mid = L.k_out;
+    if ((rc = run_gdelta(m, dt, st)) != B200_OK) return rc;
   } else if (L.mixer == B200_MIX_DELTA) {
     const int H = L.attn.heads, hd = H * L.attn.dim, rk = up8i(L.delta.rank);
     // decay logits: tanh of the bottleneck rows (T), then w2·(…) + w0 in fp32
@@ -681,10 +708,21 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     a.cache = s->kbase + s->run_k_off[r] * esz; a.slot_stride = (int64_t)s->k_slot;
     a.slot = s->m_slot; a.pos = s->m_pos; a.n_tok = n_tok;
     a.qa = s->qa; a.ol = s->ol; a.out = s->mid; a.ld_out = L.k_out;
-    if (n_tok <= kSmallRows && s->lat_ws != nullptr) {   // splits follow the context the engine was built for, not the
-      a.split_ws = s->lat_ws;                             // positions of the moment: a captured step stays valid
-      a.nsplit = std::min(kLatentMaxSplits, (d.max_ctx + kLatentSplitKeys - 1) / kLatentSplitKeys);
-      a.keys_per_split = ((d.max_ctx + a.nsplit - 1) / a.nsplit + 31) / 32 * 32;
+    const int hq = L.attn.heads * (L.attn.dim + L.lat.rot_dim);
+    if (L.lat.q_rank > 0) {   // queries through a latent of their own: q = uq·(rms(down-projected rows)·q_norm)
+      const int qr = L.lat.q_rank, qr8 = up8i(qr);
+      if ((rc = launch_stack_rmsnorm_rows(s->rec_lr, qr8, (const uint8_t*)s->proj + (size_t)L.off_q * esz, L.n_in, L.lat.q_norm, n_tok,
+                                          qr, qr8, d.norm_eps, dt, st)) != B200_OK)
+        return rc;
+      if ((rc = stack_lin(s, s->rec_lr, L.lat.uq, nullptr, n_tok, hq, qr8, pl.ok_uq ? &pl.uq : nullptr, s->latq, nullptr, st)) != B200_OK)
+        return rc;
+      a.q = s->latq; a.ld_q = hq;
+    }
+    if (n_tok <= kSmallRows && s->lat_ws != nullptr) {   // splits follow the context the engine was built for (or the window),
+      a.split_ws = s->lat_ws;                             // not the positions of the moment: a captured step stays valid
+      const int kmax = L.attn.window > 0 ? std::min(L.attn.window, d.max_ctx) : d.max_ctx;
+      a.nsplit = std::min(kLatentMaxSplits, (kmax + kLatentSplitKeys - 1) / kLatentSplitKeys);
+      a.keys_per_split = ((kmax + a.nsplit - 1) / a.nsplit + 31) / 32 * 32;
     }
     // prompts of bf16 engines whose heads suit the tensor-core attention kernel: per sequence, keys and values are expanded
     // from the cache rows by two tcgen05 products and laid out per head; what is left takes the general kernels
@@ -698,10 +736,14 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     } else {
       if ((rc = launch_latent_prep(a, dt, st)) != B200_OK) return rc;
       const __nv_bfloat16* P0 = (const __nv_bfloat16*)s->proj;
+      const bool own_q = a.q != nullptr;   // the per-head queries: their own rows, or the q segment of the projection
+      const __nv_bfloat16* Q0 = own_q ? (const __nv_bfloat16*)a.q : P0;
+      const int64_t ldq = own_q ? a.ld_q : L.n_in;
       for (const StackEngine::Seg& g : s->segs) {
         if (g.count < kTcRows) {   // a short part: the general kernels on its rows (the cache rows are written again, equal)
           LatentRun b = a;
           b.proj = P0 + (size_t)g.row0 * L.n_in;
+          if (own_q) b.q = Q0 + (size_t)g.row0 * ldq;
           b.slot = a.slot + g.row0; b.pos = a.pos + g.row0; b.n_tok = g.count;
           b.qa = (__nv_bfloat16*)s->qa + (size_t)g.row0 * Hh * (rk + L.lat.rot_dim);
           b.ol = (__nv_bfloat16*)s->ol + (size_t)g.row0 * Hh * rk;
@@ -718,16 +760,20 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
         if ((rc = launch_gemm_bf16(s->lat_v, s->lat_c, L.lat.uv, ctx, Hh * L.attn.vdim, rk, st)) != B200_OK) return rc;
         LatentPack k;
         k.a = L.attn; k.l = L.lat; k.kp = s->lat_kp; k.cache_rows = rows;
-        k.proj = P0 + (size_t)g.row0 * L.n_in; k.ld_proj = L.n_in; k.off_q = L.off_q;
+        k.proj = Q0 + (size_t)g.row0 * ldq; k.ld_proj = ldq; k.off_q = own_q ? 0 : L.off_q;
         k.qa = (const __nv_bfloat16*)s->qa + (size_t)g.row0 * Hh * kd;
         k.kbuf = s->lat_k; k.qbuf = s->lat_q; k.ctx = ctx; k.count = g.count;
         if ((rc = launch_latent_pack(k, st)) != B200_OK) return rc;
         if ((rc = launch_attn_prefill_window((__nv_bfloat16*)s->mid + (size_t)g.row0 * L.k_out, L.k_out, s->lat_q, nullptr,
-                                             (int64_t)Hh * hd, s->lat_k, s->lat_v, g.count, Hh, Hh, hd, g.pos0, L.attn.scale, 0, 0,
-                                             st)) != B200_OK)
+                                             (int64_t)Hh * hd, s->lat_k, s->lat_v, g.count, Hh, Hh, hd, g.pos0, L.attn.scale,
+                                             L.attn.window, 0, st)) != B200_OK)
           return rc;
       }
     }
+    if (L.lat.out_gate &&
+        (rc = launch_stack_sigmoid_gate(s->mid, L.k_out, (const uint8_t*)s->proj + (size_t)L.off_g * esz, L.n_in, n_tok,
+                                        L.attn.heads * L.attn.vdim, dt, st)) != B200_OK)
+      return rc;
   } else {
     MlstmRun m;
     m.a = L.attn; m.gate_cap = L.rec.gate_cap; m.eps = d.norm_eps;
@@ -744,7 +790,7 @@ static int stack_run_sandwich(StackEngine* s, int r, float* x, int n_tok, cudaSt
     if ((rc = run_mlstm(m, dt, st)) != B200_OK) return rc;
   }
   if ((rc = stack_lin_norm_add(s, s->mid, L.w_out, n_tok, L.k_out, pl.ok_out ? &pl.out : nullptr, L.post_norm, x,
-                               has_ff ? (pre ? L.ff_norm : L.post_norm) : next_run_w, st)) != B200_OK)
+                               has_ff ? (pre ? L.ff_norm : L.post_norm) : next_run_w, st, L.b_out)) != B200_OK)
     return rc;
   // ---- feed-forward
   if (!has_ff) {
@@ -1127,12 +1173,18 @@ int64_t stack_bytes_per_token(const b200_engine* e, int64_t ctx) {
         int64_t keys = ctx + 1;
         if (a.window > 0) keys = std::min<int64_t>(keys, (int64_t)a.window + a.keep_first);
         bytes += (keys + 1) * a.kv_heads * (a.dim + a.vdim) * s->esz;
+      } else if (L.mixer == B200_MIX_GATED_DELTA) {   // the state and the convolutions' inputs read and written
+        bytes += 2 * gdelta_state_floats(a.heads, a.kv_heads, a.dim, a.vdim, L.gdelta.taps) * 4;
       } else if (L.mixer == B200_MIX_DELTA) {   // the decay's second stage; the state read and written
         bytes += (int64_t)a.heads * a.dim * L.delta.rank * s->esz + 2ll * a.heads * a.dim * a.vdim * 4;
       } else if (L.mixer == B200_MIX_MAMBA2) {
         bytes += 2 * mamba_state_floats(a.heads, a.vdim, L.mamba.state, L.mamba.groups, L.mamba.taps) * 4;
-      } else if (L.mixer == B200_MIX_LATENT)   // uk, uv, the cache rows read once and one written
-        bytes += ((int64_t)a.heads * (a.dim + a.vdim) * L.lat.kv_rank + (ctx + 2) * (L.lat.kv_rank + L.lat.rot_dim)) * s->esz;
+      } else if (L.mixer == B200_MIX_LATENT) {   // uk, uv (uq), the visible cache rows read once and one written
+        int64_t keys = ctx + 1;
+        if (a.window > 0) keys = std::min<int64_t>(keys, a.window);
+        bytes += ((int64_t)a.heads * (a.dim + a.vdim) * L.lat.kv_rank + (keys + 1) * (L.lat.kv_rank + L.lat.rot_dim) +
+                  (int64_t)a.heads * (a.dim + L.lat.rot_dim) * L.lat.q_rank) * s->esz;
+      }
       else                              // the state read and written
         bytes += 2 * mlstm_state_floats(a.heads, a.dim, a.vdim) * 4;
       if (L.ff_kind == B200_FF_DENSE) bytes += 2ll * L.ff * d.width * s->esz;
@@ -1197,7 +1249,7 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
     const b200_stack_layer& L = s->layers[l];
     const b200_attn_desc& a = L.attn;
     const int W = d.width;
-    B200_CHECK_ARG(L.mixer >= B200_MIX_ATTENTION && L.mixer <= B200_MIX_MAMBA2, "engine_create_stack: layer %d: mixer kind %d is not built", l, L.mixer);
+    B200_CHECK_ARG(L.mixer >= B200_MIX_ATTENTION && L.mixer <= B200_MIX_GATED_DELTA, "engine_create_stack: layer %d: mixer kind %d is not built", l, L.mixer);
     B200_CHECK_ARG(a.heads > 0 && a.dim > 0 && a.vdim > 0, "engine_create_stack: layer %d: bad mixer sizes", l);
     B200_CHECK_ARG((L.norm || d.block == B200_BLOCK_POSTNORM) && L.post_norm && L.w_in && L.w_out && L.n_in > 0 &&
                        L.k_out == a.heads * a.vdim,
@@ -1206,9 +1258,18 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       const b200_attn_prep_desc& q = L.prep;
       B200_CHECK_ARG(a.kv_heads > 0 && a.heads % a.kv_heads == 0 && a.window >= 0 && a.keep_first >= 0 && a.vdim <= 256 && a.dim <= 1024,
                      "engine_create_stack: layer %d: bad attention sizes", l);
-      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in && L.off_k + a.kv_heads * a.dim <= L.n_in &&
-                         L.off_v + a.kv_heads * a.vdim <= L.n_in && (!a.out_gate || L.off_g + a.heads <= L.n_in),
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * a.dim <= L.n_in &&
+                         (L.kv_share > 0 || (L.off_k + a.kv_heads * a.dim <= L.n_in && L.off_v + a.kv_heads * a.vdim <= L.n_in)) &&
+                         (!a.out_gate || L.off_g + a.heads <= L.n_in),
                      "engine_create_stack: layer %d: segment offsets do not fit", l);
+      if (L.kv_share > 0) {   // the source: an earlier attention layer with projections of its own and the same cache rows
+        B200_CHECK_ARG(L.kv_share - 1 < l, "engine_create_stack: layer %d reads the keys and values of layer %d, which is not an earlier layer", l, L.kv_share - 1);
+        const b200_stack_layer& S = s->layers[L.kv_share - 1];
+        B200_CHECK_ARG(S.mixer == B200_MIX_ATTENTION && S.kv_share == 0 && S.attn.kv_heads == a.kv_heads && S.attn.dim == a.dim &&
+                           S.attn.vdim == a.vdim,
+                       "engine_create_stack: layer %d: layer %d is not an attention layer with keys and values of its own and equal sizes", l, L.kv_share - 1);
+        B200_CHECK_ARG(!q.v_norm && !q.v_mix, "engine_create_stack: layer %d: a layer without values of its own cannot norm or mix them", l);
+      }
       B200_CHECK_ARG(q.rot_dims >= 0 && q.rot_dims % 2 == 0 && q.rot_dims <= a.dim && (q.rot_dims == 0 || q.rot_table) &&
                          (!q.qk_norm || (q.q_norm && q.k_norm)) && q.v_mix >= 0 && q.v_mix <= 2 && (q.v_mix != 2 || q.mix_lambda),
                      "engine_create_stack: layer %d: attention preparation", l);
@@ -1219,6 +1280,19 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
         s->vkeep_max = a.kv_heads * a.vdim;
       }
       s->max_vdim = std::max(s->max_vdim, a.vdim);
+    } else if (L.mixer == B200_MIX_GATED_DELTA) {
+      const b200_gdelta_desc& q = L.gdelta;
+      B200_CHECK_ARG(a.dim <= kScanMaxDim && a.kv_heads > 0 && a.heads % a.kv_heads == 0 && q.taps >= 1 && q.taps <= kMambaMaxTaps &&
+                         q.conv_w && q.A_log && q.dt_bias && q.head_norm && q.unit_eps >= 0.f,
+                     "engine_create_stack: layer %d: gated delta rule description (key size up to %d, 1 … %d taps)", l, kScanMaxDim,
+                     kMambaMaxTaps);
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.kv_heads * a.dim <= L.n_in && L.off_k + a.kv_heads * a.dim <= L.n_in &&
+                         L.off_v + a.heads * a.vdim <= L.n_in && L.off_g + a.heads * a.vdim <= L.n_in &&
+                         L.off_gate + a.heads <= L.n_in && L.off_up + a.heads <= L.n_in,
+                     "engine_create_stack: layer %d: segment offsets do not fit", l);
+      s->rec_o_max = std::max(s->rec_o_max, a.heads * a.vdim);
+      s->rec_f_max = std::max(s->rec_f_max, (int)gdelta_row_floats(a.heads, a.kv_heads, a.dim, a.vdim));
+      s->any_rec = s->recurrent = true;
     } else if (L.mixer == B200_MIX_DELTA) {
       const b200_delta_desc& q = L.delta;
       B200_CHECK_ARG(a.dim <= kScanMaxDim && q.rank > 0 && q.w2 && q.w0 && q.head_norm && q.unit_eps >= 0.f,
@@ -1252,9 +1326,15 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
                          q.rot_dims % 2 == 0,
                      "engine_create_stack: layer %d: latent sizes (kv_rank 1 … %d, even rot_dims <= rot_dim)", l, kLatentMaxRank);
       B200_CHECK_ARG(q.c_norm && q.uk_t && q.uv && (q.rot_dims == 0 || q.rot_table), "engine_create_stack: layer %d: null latent weight", l);
-      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + a.heads * (a.dim + q.rot_dim) <= L.n_in && L.off_k >= 0 &&
-                         L.off_k + q.kv_rank + q.rot_dim <= L.n_in,
+      B200_CHECK_ARG(L.off_q >= 0 && L.off_q + (q.q_rank > 0 ? q.q_rank : a.heads * (a.dim + q.rot_dim)) <= L.n_in && L.off_k >= 0 &&
+                         L.off_k + q.kv_rank + q.rot_dim <= L.n_in && (!q.out_gate || L.off_g + a.heads * a.vdim <= L.n_in),
                      "engine_create_stack: layer %d: segment offsets do not fit", l);
+      B200_CHECK_ARG(q.q_rank >= 0 && (q.q_rank == 0 || (q.q_norm && q.uq)) && a.window >= 0,
+                     "engine_create_stack: layer %d: query latent without its norm or up-projection", l);
+      if (q.q_rank > 0) {
+        s->rec_lr_max = std::max(s->rec_lr_max, up8i(q.q_rank));
+        s->latq_max = std::max(s->latq_max, a.heads * (a.dim + q.rot_dim));
+      }
       s->qa_max = std::max(s->qa_max, a.heads * (q.kv_rank + q.rot_dim));
       s->ol_max = std::max(s->ol_max, a.heads * q.kv_rank);
       s->lat_heads_max = std::max(s->lat_heads_max, a.heads);
@@ -1327,6 +1407,7 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
   s->run_k_off.resize(d.n_runs);
   s->run_v_off.resize(d.n_runs);
   s->run_s_off.resize(d.n_runs);
+  s->run_kv_shared.assign(d.n_runs, 0);
   for (int r = 0; r < d.n_runs; ++r) {
     B200_CHECK_ARG(s->run_layer[r] >= 0 && s->run_layer[r] < d.n_layers, "engine_create_stack: run %d names layer %d", r,
                    s->run_layer[r]);
@@ -1336,9 +1417,21 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
     s->run_k_off[r] = s->k_slot;
     s->run_v_off[r] = s->v_slot;
     s->run_s_off[r] = s->s_slot;
-    if (RL.mixer == B200_MIX_ATTENTION) {
+    if (RL.mixer == B200_MIX_ATTENTION && sandwich && RL.kv_share > 0) {
+      // the cache of the latest earlier run of the source layer (the pass of a loop this run belongs to, or the last one)
+      int src = -1;
+      for (int q = 0; q < r; ++q)
+        if (s->run_layer[q] == RL.kv_share - 1) src = q;
+      B200_CHECK_ARG(src >= 0, "engine_create_stack: run %d reads the keys and values of layer %d, which has not run before it", r,
+                     RL.kv_share - 1);
+      s->run_k_off[r] = s->run_k_off[src];
+      s->run_v_off[r] = s->run_v_off[src];
+      s->run_kv_shared[r] = 1;
+    } else if (RL.mixer == B200_MIX_ATTENTION) {
       s->k_slot += (size_t)d.max_ctx * a.kv_heads * a.dim;
       s->v_slot += (size_t)d.max_ctx * a.kv_heads * a.vdim;
+    } else if (RL.mixer == B200_MIX_GATED_DELTA) {   // a fixed-size state and the convolutions' last inputs
+      s->s_slot += (size_t)gdelta_state_floats(a.heads, a.kv_heads, a.dim, a.vdim, RL.gdelta.taps);
     } else if (RL.mixer == B200_MIX_LATENT) {   // one row per position: [latent | rotated shared key part]
       s->k_slot += (size_t)d.max_ctx * (RL.lat.kv_rank + RL.lat.rot_dim);
     } else if (RL.mixer == B200_MIX_DELTA) {    // no rows per position: a fixed-size state
@@ -1381,6 +1474,8 @@ static int stack_build(const b200_stack_desc* desc, b200_engine** out) {
       sp.ok_out = plan(&sp.out, L.w_out, d.width, L.k_out, EPI_BIAS_F32);
       if (L.mixer == B200_MIX_DELTA)
         sp.ok_lora = plan(&sp.lora, L.delta.w2, (int64_t)L.attn.heads * L.attn.dim, up8i(L.delta.rank), EPI_BIAS_F32);
+      if (L.mixer == B200_MIX_LATENT && L.lat.q_rank > 0)
+        sp.ok_uq = plan(&sp.uq, L.lat.uq, (int64_t)L.attn.heads * (L.attn.dim + L.lat.rot_dim), up8i(L.lat.q_rank), EPI_BIAS_F32);
       if (L.ff_kind == B200_FF_DENSE && L.ff > 0) {
         sp.ok_ff_in = plan(&sp.ff_in, L.w_ff_in, L.ff, d.width, EPI_BIAS_F32);
         sp.ok_ff_out = plan(&sp.ff_out, L.w_ff_out, d.width, L.ff, EPI_BIAS_F32);

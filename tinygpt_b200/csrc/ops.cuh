@@ -61,7 +61,7 @@ int launch_attn_prefill_mma(void* o, const void* qkv, const void* kcache, const 
                             int p0, cudaStream_t st);
 int launch_attn_prefill_window(void* o, int64_t o_rs, const void* q, const void* gate_or_null, int64_t q_rs,
                                const void* kcache, const void* vcache, int S, int Hq, int Hkv, int hd, int p0, float scale,
-                               int window, int keep_first, cudaStream_t st);
+                               int window, int keep_first, cudaStream_t st, int sink = 0);
 int launch_attn_causal_mma(void* o, const void* q, const void* k, const void* v, int64_t B, int64_t S, int64_t Hq,
                            int64_t Hkv, int64_t hd, cudaStream_t st);
 

@@ -78,6 +78,7 @@ struct PrefillAttnParams {
   // j <= i and (window == 0 or i − j < window or j < keep_first)
   int window, keep_first;
   const __nv_bfloat16* gate;    // per-head gate logits, head h of row r at gate + b*q_bs + r*q_rs + h; null = none
+  int sink;                     // 1: the softmax's denominator gains 1 (a key of score 0 that has no value)
 };
 
 // byte offset of 16-byte chunk c of row r inside a [rows][HD] bf16 tile (chunks XOR-swizzled within groups of 8)
@@ -268,6 +269,7 @@ __global__ void __launch_bounds__(kPfThreads) attn_prefill_mma_kernel(const Pref
     float l = l_run[rr];
     l += __shfl_xor_sync(0xffffffffu, l, 1);
     l += __shfl_xor_sync(0xffffffffu, l, 2);
+    if (p.sink && m_run[rr] != -INFINITY) l += exp2f(-m_run[rr] * kScale);
     float inv = l > 0.f ? 1.f / l : 0.f;
     const int r = warp * 16 + g + 8 * rr;
     if (r < rows_valid) {
@@ -329,7 +331,7 @@ int launch_attn_prefill_mma(void* o, const void* qkv, const void* kcache, const 
 // gate logits) are column ranges of the merged projection rows (stride q_rs), o a column range of rows of stride o_rs.
 int launch_attn_prefill_window(void* o, int64_t o_rs, const void* q, const void* gate_or_null, int64_t q_rs,
                                const void* kcache, const void* vcache, int S, int Hq, int Hkv, int hd, int p0, float scale,
-                               int window, int keep_first, cudaStream_t st) {
+                               int window, int keep_first, cudaStream_t st, int sink) {
   B200_CHECK_ARG(hd == 64 || hd == 128, "prefill attention: head size %d not built", hd);
   B200_CHECK_ARG(S > 0 && Hkv > 0 && Hq % Hkv == 0 && Hq < 65536 && p0 >= 0 && window >= 0 && keep_first >= 0,
                  "prefill attention: bad shape");
@@ -352,6 +354,7 @@ int launch_attn_prefill_window(void* o, int64_t o_rs, const void* q, const void*
   p.scale_log2 = scale * kLog2eP;
   p.window = window;
   p.keep_first = keep_first;
+  p.sink = sink;
   return hd == 64 ? launch_pf<64>(p, 1, st) : launch_pf<128>(p, 1, st);
 }
 

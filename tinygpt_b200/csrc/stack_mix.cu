@@ -3,6 +3,7 @@
 // Every kernel starts with griddepcontrol.launch_dependents + griddepcontrol.wait (programmatic dependent launch).
 #include "stack_mix.cuh"
 
+#include <algorithm>
 #include <vector>
 
 #include "ops.cuh"
@@ -145,9 +146,44 @@ __global__ void __launch_bounds__(256) stack_softcap_kernel(float* __restrict__ 
   }
 }
 
+// y[r, :dim] = T(rms(x[r, :dim])·w), y[r, dim:dim_pad] = 0 over row-strided T-typed rows (a latent's norm between two products)
+template <typename T>
+__global__ void __launch_bounds__(128) stack_rmsnorm_rows_kernel(T* __restrict__ y, int64_t ld_y, const T* __restrict__ x,
+                                                                 int64_t ld_x, const float* __restrict__ w, int dim, int dim_pad,
+                                                                 float eps) {
+  pdl_trigger();
+  pdl_wait();
+  __shared__ float red[4];
+  const T* xr = x + (int64_t)blockIdx.x * ld_x;
+  T* yr = y + (int64_t)blockIdx.x * ld_y;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float v = ldf<T>(xr + i);
+    ss += v * v;
+  }
+  const float inv = rsqrtf(block_sum(ss, red) / (float)dim + eps);
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) yr[i] = cvt<T>(ldf<T>(xr + i) * inv * w[i]);
+  for (int i = dim + threadIdx.x; i < dim_pad; i += blockDim.x) yr[i] = cvt<T>(0.f);
+}
+
+// y[r, j] = T(y[r, j]·sigmoid(g[r, j])) over row-strided operands (an element-wise output gate)
+template <typename T>
+__global__ void __launch_bounds__(256) stack_sigmoid_gate_kernel(T* __restrict__ y, int64_t ld_y, const T* __restrict__ g,
+                                                                 int64_t ld_g, int n, int64_t total) {
+  pdl_trigger();
+  pdl_wait();
+  for (int64_t e = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t r = e / n;
+    const int j = (int)(e % n);
+    T* dst = y + r * ld_y + j;
+    *dst = cvt<T>(ldf<T>(dst) / (1.f + expf(-ldf<T>(g + r * ld_g + j))));
+  }
+}
+
 // --------------------------------------------------------------------------------------------------- latent attention
 // One CTA per new token: the latent c = rms(down[:r])·c_norm and the rotated shared key part go into the slot's cache
-// row of the token's position; the rotated part of every head's query goes behind that head's folded query in qa.
+// row of the token's position; the rotated part of every head's query goes behind that head's folded query in qa.  Pair i of
+// the first rot_dims entries is (2i, 2i+1), or — rot_half — (i, i + rot_dims/2); the entries behind them pass unchanged.
 template <typename T>
 __global__ void __launch_bounds__(128) latent_prep_kernel(const LatentRun p) {
   pdl_trigger();
@@ -156,6 +192,7 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const LatentRun p) {
   const int t = blockIdx.x;
   const int r = p.l.kv_rank, dr = p.l.rot_dim, kd = r + dr, dn = p.a.dim, half = p.l.rot_dims / 2;
   const T* row = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
+  const T* qrow = static_cast<const T*>(p.q) + (int64_t)t * p.ld_q;
   const T* down = row + p.off_down;
   const int pos = p.pos[t];
   T* crow = static_cast<T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride + (int64_t)pos * kd;
@@ -167,26 +204,23 @@ __global__ void __launch_bounds__(128) latent_prep_kernel(const LatentRun p) {
   const float inv = rsqrtf(block_sum(ss, red) / (float)r + p.eps);
   for (int i = threadIdx.x; i < r; i += blockDim.x) crow[i] = cvt<T>(ldf<T>(down + i) * inv * p.l.c_norm[i]);
   const float* cs = p.l.rot_table + (int64_t)pos * half * 2;
-  // rotated vectors: index 0 the shared key part, 1 … heads the queries' rotated parts
-  const int per = (dr + 1) / 2;   // pairs (the last one may be a single unrotated entry)
+  // rotated vectors: index 0 the shared key part, 1 … heads the queries' rotated parts; per vector `half` pairs, then the
+  // dr − 2·half entries that do not turn
+  const int per = half + (dr - 2 * half);
   for (int e = threadIdx.x; e < (p.a.heads + 1) * per; e += blockDim.x) {
     const int which = e / per, i = e % per;
-    const T* src = which == 0 ? down + r : row + p.off_q + (int64_t)(which - 1) * (dn + dr) + dn;
+    const T* src = which == 0 ? down + r : qrow + (int64_t)(which - 1) * (dn + dr) + dn;
     T* dst = which == 0 ? crow + r : static_cast<T*>(p.qa) + (int64_t)t * p.a.heads * kd + (int64_t)(which - 1) * kd + r;
-    const float u = ldf<T>(src + 2 * i);
-    if (2 * i + 1 >= dr) {
-      dst[2 * i] = cvt<T>(u);
+    if (i >= half) {
+      const int c = 2 * half + (i - half);
+      dst[c] = cvt<T>(ldf<T>(src + c));
       continue;
     }
-    const float v = ldf<T>(src + 2 * i + 1);
-    if (i < half) {
-      const float c = cs[2 * i], s = cs[2 * i + 1];
-      dst[2 * i] = cvt<T>(u * c - v * s);
-      dst[2 * i + 1] = cvt<T>(v * c + u * s);
-    } else {
-      dst[2 * i] = cvt<T>(u);
-      dst[2 * i + 1] = cvt<T>(v);
-    }
+    const int ia = p.l.rot_half ? i : 2 * i, ib = p.l.rot_half ? i + half : 2 * i + 1;
+    const float u = ldf<T>(src + ia), v = ldf<T>(src + ib);
+    const float c = cs[2 * i], sn = cs[2 * i + 1];
+    dst[ia] = cvt<T>(u * c - v * sn);
+    dst[ib] = cvt<T>(v * c + u * sn);
   }
 }
 
@@ -208,11 +242,12 @@ __global__ void __launch_bounds__(128) latent_attn_kernel(const LatentRun p) {
   for (int i = threadIdx.x; i < kd; i += blockDim.x) q[i] = ldf<T>(qrow + i) * p.a.scale;
   __syncthreads();
   const int n_keys = p.pos[t] + 1;
+  const int k_first = p.a.window > 0 ? max(0, n_keys - p.a.window) : 0;   // the window's first key
   const T* K = static_cast<const T*>(p.cache) + (int64_t)p.slot[t] * p.slot_stride;
   float m = -INFINITY, sum = 0.f, acc[VR];
 #pragma unroll
   for (int i = 0; i < VR; ++i) acc[i] = 0.f;
-  for (int j0 = warp * 32; j0 < n_keys; j0 += 128) {
+  for (int j0 = k_first + warp * 32; j0 < n_keys; j0 += 128) {
     const int cnt = min(32, n_keys - j0);
     float s_mine = -INFINITY;
     for (int jj = 0; jj < cnt; ++jj) {
@@ -278,7 +313,7 @@ __global__ void __launch_bounds__(128) latent_pack_kernel(const LatentPack p) {
     }
   } else {
     const int t = row - p.ctx;
-    const __nv_bfloat16* q = p.proj + (int64_t)t * p.ld_proj + p.off_q;
+    const __nv_bfloat16* q = p.proj + (int64_t)t * p.ld_proj + p.off_q;   // the caller points proj / ld_proj / off_q at the query rows
     const __nv_bfloat16* qa = p.qa + (int64_t)t * H * kd;
     __nv_bfloat16* dst = p.qbuf + (int64_t)t * H * hd;
     for (int i = threadIdx.x; i < H * hd; i += blockDim.x) {
@@ -373,7 +408,8 @@ __global__ void __launch_bounds__(256) latent_attn_split_kernel(const LatentRun 
   float* kc = sm + (size_t)H * kd;        // [32][kd] staged key rows
   const T* qrow = static_cast<const T*>(p.qa) + (int64_t)t * H * kd;
   const int n_keys = p.pos[t] + 1;
-  const int k_lo = split * p.keys_per_split, k_hi = min(n_keys, k_lo + p.keys_per_split);
+  const int k_first = p.a.window > 0 ? max(0, n_keys - p.a.window) : 0;   // the window's first key: split 0 starts there
+  const int k_lo = k_first + split * p.keys_per_split, k_hi = min(n_keys, k_lo + p.keys_per_split);
   if (k_lo >= n_keys) return;   // the merge reads the splits that saw a key, and only those
   if (p.stage_vec) {
     for (int i = threadIdx.x * 8; i < H * kd; i += blockDim.x * 8) {
@@ -487,7 +523,8 @@ __global__ void __launch_bounds__(256) latent_merge_kernel(const LatentRun p) {
   __shared__ float s_tot;
   const int t = blockIdx.x, hd = blockIdx.y, H = p.a.heads, r = p.l.kv_rank;
   const float* src = p.split_ws + ((int64_t)t * H + hd) * p.nsplit * (2 + r);
-  const int used = min(p.nsplit, (p.pos[t] + p.keys_per_split) / p.keys_per_split);   // splits that saw a key
+  const int visible = p.a.window > 0 ? min(p.pos[t] + 1, p.a.window) : p.pos[t] + 1;
+  const int used = min(p.nsplit, (visible + p.keys_per_split - 1) / p.keys_per_split);   // splits that saw a key
   if (threadIdx.x < 32) {
     const int lane = threadIdx.x;
     float mx[kLatentMaxSplits / 32], sm_[kLatentMaxSplits / 32], M = -INFINITY;
@@ -935,16 +972,55 @@ int launch_latent_pack(const LatentPack& p, cudaStream_t st) {
   return B200_OK;
 }
 
-int launch_latent_prep(const LatentRun& p, int dtype, cudaStream_t st) {
+int launch_stack_rmsnorm_rows(void* y, int64_t ld_y, const void* x, int64_t ld_x, const float* w, int64_t rows, int dim, int dim_pad,
+                              float eps, int dtype, cudaStream_t st) {
   MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(y && x && w && rows > 0 && dim > 0 && ld_y >= std::max(dim, dim_pad) && ld_x >= dim, "stack rmsnorm rows: bad arguments");
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_rmsnorm_rows_kernel<float>, dim3((unsigned)rows), dim3(128), 0, st, stack_pdl(), (float*)y, ld_y,
+                         (const float*)x, ld_x, w, dim, dim_pad, eps));
+  else
+    B200_CUDA(launch_pdl(stack_rmsnorm_rows_kernel<__nv_bfloat16>, dim3((unsigned)rows), dim3(128), 0, st, stack_pdl(),
+                         (__nv_bfloat16*)y, ld_y, (const __nv_bfloat16*)x, ld_x, w, dim, dim_pad, eps));
+  return B200_OK;
+}
+
+int launch_stack_sigmoid_gate(void* y, int64_t ld_y, const void* g, int64_t ld_g, int64_t rows, int n, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(y && g && rows > 0 && n > 0 && ld_y >= n && ld_g >= n, "stack sigmoid gate: bad arguments");
+  const int64_t total = rows * n;
+  const unsigned grid = (unsigned)std::min<int64_t>((total + 255) / 256, 4 * 148);
+  if (dtype == B200_F32)
+    B200_CUDA(launch_pdl(stack_sigmoid_gate_kernel<float>, dim3(grid), dim3(256), 0, st, stack_pdl(), (float*)y, ld_y,
+                         (const float*)g, ld_g, n, total));
+  else
+    B200_CUDA(launch_pdl(stack_sigmoid_gate_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, st, stack_pdl(), (__nv_bfloat16*)y,
+                         ld_y, (const __nv_bfloat16*)g, ld_g, n, total));
+  return B200_OK;
+}
+
+// the per-head query rows: the caller's, or the q segment of the merged projection
+static LatentRun latent_with_q(const LatentRun& p, int dtype) {
+  LatentRun q = p;
+  if (q.q == nullptr) {
+    q.q = (const uint8_t*)p.proj + (size_t)p.off_q * (dtype == B200_F32 ? 4 : 2);
+    q.ld_q = p.ld_proj;
+  }
+  return q;
+}
+
+int launch_latent_prep(const LatentRun& p0, int dtype, cudaStream_t st) {
+  MIX_DTYPE_CHECK(dtype);
+  const LatentRun p = latent_with_q(p0, dtype);
   B200_CHECK_ARG(p.proj && p.cache && p.slot && p.pos && p.qa && p.n_tok > 0, "latent prep: null argument");
   if (dtype == B200_F32) B200_CUDA(launch_pdl(latent_prep_kernel<float>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(latent_prep_kernel<__nv_bfloat16>, dim3(p.n_tok), dim3(128), 0, st, stack_pdl(), p));
   return B200_OK;
 }
 
-int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
+int run_latent_attention(const LatentRun& p0, int dtype, cudaStream_t st) {
   MIX_DTYPE_CHECK(dtype);
+  const LatentRun p = latent_with_q(p0, dtype);
   const int r = p.l.kv_rank, dr = p.l.rot_dim, H = p.a.heads, dn = p.a.dim, kd = r + dr;
   B200_CHECK_ARG(p.proj && p.cache && p.slot && p.pos && p.qa && p.ol && p.out && p.n_tok > 0, "latent attention: null argument");
   B200_CHECK_ARG(H > 0 && dn > 0 && p.a.vdim > 0 && r > 0 && dr >= 0 && p.l.rot_dims >= 0 && p.l.rot_dims <= dr &&
@@ -960,14 +1036,14 @@ int run_latent_attention(const LatentRun& p, int dtype, cudaStream_t st) {
   // folded query of head h = uk_hᵀ · q_plain of head h
   if (small) {
     SmallGemv g;
-    g.a = (const uint8_t*)p.proj + (size_t)p.off_q * esz; g.lda = p.ld_proj; g.sa = dn + dr;
+    g.a = p.q; g.lda = p.ld_q; g.sa = dn + dr;
     g.w = p.l.uk_t; g.sw = (int64_t)r * dn;
     g.c = p.qa; g.ldc = (int64_t)H * kd; g.sc = kd;
     g.M = p.n_tok; g.N = r; g.K = dn; g.items = H;
     if ((rc = launch_small_gemv(g, dtype, st)) != B200_OK) return rc;
   } else {
     StackGemm g;
-    g.a = (const uint8_t*)p.proj + (size_t)p.off_q * esz; g.lda = p.ld_proj; g.k1 = dn; g.sa = dn + dr;
+    g.a = p.q; g.lda = p.ld_q; g.k1 = dn; g.sa = dn + dr;
     g.w = p.l.uk_t; g.sw = (int64_t)r * dn;
     g.M = p.n_tok; g.N = r; g.K = dn; g.batch = H;
     g.epi = SEPI_STORE; g.c = p.qa; g.ldc = (int64_t)H * kd; g.sc = kd;

@@ -22,6 +22,12 @@ int launch_stack_glu_clamp(void* y, int64_t ld_y, const void* gu, int64_t ld_gu,
 // logits (fp32) and their bf16 copy <- cap·tanh(logits / cap)
 int launch_stack_softcap(float* logits, __nv_bfloat16* logits_bf, int64_t total, float cap, cudaStream_t st);
 
+// y[r, :dim] = T(rms(x[r, :dim])·w), y[r, dim:dim_pad] = 0 over row-strided T-typed rows
+int launch_stack_rmsnorm_rows(void* y, int64_t ld_y, const void* x, int64_t ld_x, const float* w, int64_t rows, int dim, int dim_pad,
+                              float eps, int dtype, cudaStream_t st);
+// y[r, j] = T(y[r, j]·sigmoid(g[r, j])) over row-strided T-typed operands
+int launch_stack_sigmoid_gate(void* y, int64_t ld_y, const void* g, int64_t ld_g, int64_t rows, int n, int dtype, cudaStream_t st);
+
 // ---- small products of decode-shaped steps: `items` independent products of up to 8 rows each, one warp per output row.
 // Item z multiplies rows a + m·lda + (z / item_div)·sa (m < M) with matrix w + (item_mat ? item_mat[z] : z)·sw ([N, K] row-major) into
 // c + m·ldc + z·sc (T, or fp32 when c_f32).  Serves the per-head folds of latent attention, router and gate logits, and
@@ -60,6 +66,8 @@ struct LatentRun {
   const void* proj = nullptr;    // [n_tok, ld_proj] T: q at off_q (heads·(dim + rot_dim)), down at off_down (kv_rank + rot_dim)
   int64_t ld_proj = 0;
   int off_q = 0, off_down = 0;
+  const void* q = nullptr;       // [n_tok, ld_q] T: the per-head queries when they are not the q segment of proj (queries that
+  int64_t ld_q = 0;              // went through a latent of their own); null: proj + off_q
   void* cache = nullptr;         // this run's rows of slot 0: [max_ctx][kv_rank + rot_dim] T; slot s is s·slot_stride further
   int64_t slot_stride = 0;
   const int32_t* slot = nullptr;

@@ -287,7 +287,8 @@ __device__ __forceinline__ void stack_attn_merge_pair(const StackAttn& p, int64_
   const float l1 = s1 < p.nsplit ? __ldcg(base + (size_t)s1 * (2 + vdim) + 1) : 0.f;
   const float mt = warp_max(fmaxf(m0, m1));
   const float f0 = m0 == -INFINITY ? 0.f : expf(m0 - mt), f1 = m1 == -INFINITY ? 0.f : expf(m1 - mt);
-  const float l = warp_sum(l0 * f0 + l1 * f1);
+  float l = warp_sum(l0 * f0 + l1 * f1);
+  if (p.a.sink) l += expf(-mt);   // the sink: a key of score 0 that has no value
   const T* prow = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj;
   float gate = 1.f;
   if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
@@ -469,6 +470,7 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
     if (wi != 0) return;
     float mt = -INFINITY;
     for (int w = 0; w < NW; ++w) mt = fmaxf(mt, sc[w * (2 + vdim)]);
+    m = mt;
     l = 0.f;
 #pragma unroll
     for (int r = 0; r < NA; ++r) acc[r] = 0.f;
@@ -501,6 +503,7 @@ __global__ void __launch_bounds__(128) stack_attn_kernel(const StackAttn p) {
   float gate = 1.f;
   if (p.a.out_gate) gate = 1.f / (1.f + expf(-ldf<T>(prow + p.off_g + h)));
   T* orow = static_cast<T*>(p.out) + (int64_t)t * p.ld_out + (int64_t)h * vdim;
+  if (p.a.sink) l += expf(-m);   // the sink: a key of score 0 that has no value
   const float fin = gate / l;
   cols([&](int d, float& a) { orow[d] = cvt<T>(a * fin); });
 }

@@ -33,7 +33,8 @@ __device__ __forceinline__ float softplusf(float z) { return fmaxf(z, 0.f) + log
 
 // ------------------------------------------------------------------------------------------------ attention preparation
 // One CTA per token.  q and k: the sum of squares over the WHOLE projection (all heads), the weight of that entry, then the
-// rotation of the first rot_dims entries of every head (entry i with entry i + rot_dims/2).  v: every head by its own root
+// rotation of the first rot_dims entries of every head (entry i with entry i + rot_dims/2, or — rot_interleaved — entry 2i
+// with entry 2i + 1).  v: every head by its own root
 // mean square, then the mix with the kept values.  All in fp32 from the T-typed projection, written back as T once.
 template <typename T>
 __global__ void __launch_bounds__(256) attn_prep_kernel(const AttnPrep p) {
@@ -45,7 +46,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const AttnPrep p) {
   const int half = p.d.rot_dims / 2, items = dk - half;   // per head: `half` pairs, then the entries from rot_dims on
   T* row = static_cast<T*>(p.proj) + (int64_t)t * p.ld_proj;
   const float* tab = half > 0 ? p.d.rot_table + (int64_t)p.pos[t] * half * 2 : nullptr;
-  for (int which = 0; which < 2; ++which) {
+  for (int which = 0; which < (p.q_only ? 1 : 2); ++which) {
     T* x = row + (which ? p.off_k : p.off_q);
     const int n = (which ? G : H) * dk, nh = which ? G : H;
     const float* w = which ? p.d.k_norm : p.d.q_norm;
@@ -62,7 +63,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const AttnPrep p) {
     for (int e = tid; e < nh * items; e += 256) {
       const int hd = e / items, j = e % items;
       if (j < half) {
-        const int i0 = hd * dk + j, i1 = i0 + half;
+        const int i0 = hd * dk + (p.d.rot_interleaved ? 2 * j : j), i1 = i0 + (p.d.rot_interleaved ? 1 : half);
         float a = ldf<T>(x + i0) * inv, b = ldf<T>(x + i1) * inv;
         if (p.d.qk_norm) {
           a *= w[i0];
@@ -77,7 +78,7 @@ __global__ void __launch_bounds__(256) attn_prep_kernel(const AttnPrep p) {
       }
     }
   }
-  if (!p.d.v_norm && p.d.v_mix == 0) return;
+  if ((!p.d.v_norm && p.d.v_mix == 0) || p.q_only) return;
   T* v = row + p.off_v;
   T* keep = p.vkeep != nullptr ? static_cast<T*>(p.vkeep) + (int64_t)t * p.ld_keep : nullptr;
   const float lam = p.d.v_mix == 2 ? p.d.mix_lambda[0] : 0.f;
@@ -146,7 +147,7 @@ __global__ void __launch_bounds__(256, 2) lin_scan_kernel(const LinScan p) {
   const float* src_b = p.b + (int64_t)hs * dk;
   const float* src_r = p.r + (int64_t)hs * dk;
   const float* src_p = REMOVE ? p.p + (int64_t)hd * dk : nullptr;
-  const float* src_q = REMOVE ? p.q + (int64_t)hd * dk : nullptr;
+  const float* src_q = REMOVE ? p.q + (int64_t)(p.q_shared ? hs : hd) * dk : nullptr;
   float r_x[NQ], r_v[NVR];
   auto fetch = [&](int c0) {
 #pragma unroll
@@ -401,6 +402,119 @@ __global__ void __launch_bounds__(256) mamba_out_kernel(const MambaRun p) {
   }
 }
 
+// ------------------------------------------------------------------------------------------------- gated delta rule
+// Channel c of the convolved q | k | v → its column in the projection rows
+__device__ __forceinline__ int gdelta_col(const GatedDeltaRun& p, int c, int nqk) {
+  return c < nqk ? p.off_q + c : c < 2 * nqk ? p.off_k + (c - nqk) : p.off_v + (c - 2 * nqk);
+}
+
+// One CTA per token.  First every channel of q | k | v: the short causal convolution over the row's own input and the
+// taps − 1 before it (rows of the same sequence in this step, else the slot's state; zeros before position 0), then SiLU,
+// into shared memory.  Then one warp per head: q and k heads become unit vectors (q also times dim^(−1/2)); value heads get
+// their write strength beta = sigmoid(·) and decay g = exp(−exp(A_log)·softplus(· + dt_bias)).  The scan's fp32 rows:
+//   [g: H | beta·g·k (the removal's weight vector): H·dk | k: G·dk | q: G·dk | v: H·dv | beta: H]
+// The state is only READ here (gdelta_out_kernel, a later launch, moves it on).
+template <typename T>
+__global__ void __launch_bounds__(256) gdelta_prep_kernel(const GatedDeltaRun p) {
+  pdl_trigger();
+  pdl_wait();
+  extern __shared__ float sm[];   // [2·G·dk + H·dv] convolved channels
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.a.heads, G = p.a.kv_heads, dk = p.a.dim, dv = p.a.vdim, taps = p.d.taps;
+  const int nqk = G * dk, ch = 2 * nqk + H * dv;
+  const int32_t *slot = p.scan.slot, *pos = p.scan.pos;
+  const T* proj = static_cast<const T*>(p.proj);
+  const float* cs = p.conv_state + (int64_t)slot[t] * p.scan.slot_stride;
+  int in_step = 0;   // rows of this sequence in front of row t, counted up to taps − 1
+  while (in_step < taps - 1 && same_seq(slot, pos, t, in_step + 1)) ++in_step;
+  for (int c = tid; c < ch; c += 256) {
+    const int col = gdelta_col(p, c, nqk);
+    float acc = 0.f;
+    for (int j = 0; j < taps; ++j) {   // j positions back; weight column taps − 1 − j
+      float v = 0.f;
+      if (j <= in_step) v = ldf<T>(proj + (int64_t)(t - j) * p.ld_proj + col);
+      else if (pos[t] - j >= 0) v = cs[(int64_t)(taps - 1 - (j - in_step)) * ch + c];
+      acc = fmaf(p.d.conv_w[(int64_t)c * taps + taps - 1 - j], v, acc);
+    }
+    sm[c] = siluf(acc);
+  }
+  __syncthreads();
+  float* f = p.f + (int64_t)t * p.scan.ld;
+  float* f_g = f;
+  float* f_p = f + H;
+  float* f_k = f_p + (int64_t)H * dk;
+  float* f_q = f_k + nqk;
+  float* f_v = f_q + nqk;
+  float* f_beta = f_v + (int64_t)H * dv;
+  // unit query / key heads
+  for (int u = warp; u < 2 * G; u += 8) {
+    const float* x = sm + (int64_t)u * dk;   // q heads first, then k heads
+    float ss = 0.f;
+    for (int i = lane; i < dk; i += 32) ss += x[i] * x[i];
+    float inv = 1.f / sqrtf(warp_sum(ss) + p.d.unit_eps);
+    if (u < G) inv *= rsqrtf((float)dk);
+    float* dst = u < G ? f_q + (int64_t)u * dk : f_k + (int64_t)(u - G) * dk;
+    for (int i = lane; i < dk; i += 32) dst[i] = x[i] * inv;
+  }
+  __syncthreads();   // f_k of this row is read below
+  const T* row = proj + (int64_t)t * p.ld_proj;
+  for (int hd = warp; hd < H; hd += 8) {
+    const float beta = sigmoidf(ldf<T>(row + p.off_b + hd));
+    const float g = expf(-expf(p.d.A_log[hd]) * softplusf(ldf<T>(row + p.off_a + hd) + p.d.dt_bias[hd]));
+    if (lane == 0) {
+      f_g[hd] = g;
+      f_beta[hd] = beta;
+    }
+    const float* k = f_k + (int64_t)(hd / (H / G)) * dk;
+    for (int i = lane; i < dk; i += 32) f_p[(int64_t)hd * dk + i] = beta * g * k[i];
+    for (int i = lane; i < dv; i += 32) f_v[(int64_t)hd * dv + i] = sm[2 * nqk + hd * dv + i];
+  }
+}
+
+// First CTA of a token: one warp per head, o / rms(o) · head_norm (shared by the heads) · silu(out gate).  The other CTAs of a
+// sequence's LAST row in the step move the slot's convolution state on: the last taps − 1 inputs, from the step's rows where
+// it has that many, else from the old state shifted in place.
+template <typename T>
+__global__ void __launch_bounds__(256) gdelta_out_kernel(const GatedDeltaRun p) {
+  pdl_trigger();
+  pdl_wait();
+  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.a.heads, G = p.a.kv_heads, dk = p.a.dim, dv = p.a.vdim;
+  if (blockIdx.y > 0) {
+    const int32_t *slot = p.scan.slot, *pos = p.scan.pos;
+    const int taps = p.d.taps, nqk = G * dk, ch = 2 * nqk + H * dv;
+    const bool last = t + 1 >= p.scan.n_tok || slot[t + 1] != slot[t] || pos[t + 1] != pos[t] + 1;
+    if (last && taps > 1) {
+      int in_step = 0;
+      while (in_step < taps - 1 && same_seq(slot, pos, t, in_step + 1)) ++in_step;
+      float* cs = p.conv_state + (int64_t)slot[t] * p.scan.slot_stride;
+      const T* proj = static_cast<const T*>(p.proj);
+      for (int c = (blockIdx.y - 1) * 256 + tid; c < ch; c += 256 * (gridDim.y - 1)) {
+        const int col = gdelta_col(p, c, nqk);
+        // new entry i = the input taps − 2 − i positions back from row t: a step row, or the old entry i + 1 + in_step — always
+        // further along than anything written so far, so the shift runs in place
+        for (int i = 0; i < taps - 1; ++i) {
+          const int j = taps - 2 - i;
+          float v = 0.f;
+          if (j <= in_step) v = ldf<T>(proj + (int64_t)(t - j) * p.ld_proj + col);
+          else if (pos[t] - j >= 0) v = cs[(int64_t)(i + 1 + in_step) * ch + c];
+          cs[(int64_t)i * ch + c] = v;
+        }
+      }
+    }
+    return;
+  }
+  const T* g = static_cast<const T*>(p.proj) + (int64_t)t * p.ld_proj + p.off_g;
+  T* y = static_cast<T*>(p.mid) + (int64_t)t * p.ld_mid;
+  for (int hd = warp; hd < H; hd += 8) {
+    const float* o = p.scan.o + (int64_t)t * p.scan.ld_o + hd * dv;
+    float ss = 0.f;
+    for (int c = lane; c < dv; c += 32) ss += o[c] * o[c];
+    const float inv = 1.f / sqrtf(warp_sum(ss) / (float)dv + p.eps);
+    for (int c = lane; c < dv; c += 32) y[hd * dv + c] = cvt<T>(o[c] * inv * p.d.head_norm[c] * siluf(ldf<T>(g + hd * dv + c)));
+  }
+}
+
 // --------------------------------------------------------------------------------- post-norm + residual + operand copy
 template <typename YT>
 __global__ void __launch_bounds__(256) stack_rms_add_cast_kernel(float* __restrict__ x, const YT* __restrict__ y,
@@ -518,6 +632,38 @@ int run_delta(const DeltaRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(p.d.head_norm != nullptr, "delta rule: null head norm");
   if (dtype == B200_F32) B200_CUDA(launch_pdl(delta_out_kernel<float>, grid, dim3(128), 0, st, stack_pdl(), p));
   else B200_CUDA(launch_pdl(delta_out_kernel<__nv_bfloat16>, grid, dim3(128), 0, st, stack_pdl(), p));
+  return B200_OK;
+}
+
+int run_gdelta(const GatedDeltaRun& p, int dtype, cudaStream_t st) {
+  REC_DTYPE_CHECK(dtype);
+  B200_CHECK_ARG(p.proj && p.conv_state && p.f && p.mid && p.scan.n_tok > 0 && p.scan.n_seg > 0, "gated delta rule: null argument");
+  const int H = p.a.heads, G = p.a.kv_heads, dk = p.a.dim, dv = p.a.vdim;
+  B200_CHECK_ARG(H > 0 && G > 0 && H % G == 0 && dk > 0 && dv > 0, "gated delta rule: heads %d over %d query / key heads", H, G);
+  B200_CHECK_ARG(p.d.taps >= 1 && p.d.taps <= kMambaMaxTaps, "gated delta rule: 1 … %d convolution taps", kMambaMaxTaps);
+  B200_CHECK_ARG(p.d.conv_w && p.d.A_log && p.d.dt_bias && p.d.head_norm && p.d.unit_eps >= 0.f, "gated delta rule: null weight");
+  const int nqk = G * dk, ch = 2 * nqk + H * dv;
+  const size_t smem = (size_t)ch * 4;
+  B200_CHECK_ARG(smem <= 200 * 1024, "gated delta rule: %d convolved channels exceed one CTA's shared memory", ch);
+  if (smem > 48 * 1024) {
+    static bool attr_done = false;
+    if (!attr_done) {
+      B200_CUDA(cudaFuncSetAttribute(gdelta_prep_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      B200_CUDA(cudaFuncSetAttribute(gdelta_prep_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr_done = true;
+    }
+  }
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(gdelta_prep_kernel<float>, dim3(p.scan.n_tok), dim3(256), smem, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(gdelta_prep_kernel<__nv_bfloat16>, dim3(p.scan.n_tok), dim3(256), smem, st, stack_pdl(), p));
+  LinScan s = p.scan;
+  s.heads = H; s.dk = dk; s.dv = dv; s.share = H / G; s.d_scalar = 1; s.q_shared = 1;
+  s.d = p.f; s.p = p.f + H; s.q = s.p + (int64_t)H * dk; s.b = s.q; s.r = s.q + nqk; s.v = s.r + nqk;
+  s.vscale = s.v + (int64_t)H * dv;
+  int rc = launch_lin_scan(s, st);
+  if (rc != B200_OK) return rc;
+  const dim3 og(p.scan.n_tok, p.d.taps > 1 ? 1 + std::min((ch + 255) / 256, 16) : 1);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(gdelta_out_kernel<float>, og, dim3(256), 0, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(gdelta_out_kernel<__nv_bfloat16>, og, dim3(256), 0, st, stack_pdl(), p));
   return B200_OK;
 }
 

@@ -21,6 +21,7 @@ struct AttnPrep {
   int n_tok = 0;
   void* vkeep = nullptr;         // [n_tok, ld_keep] T: the values a v_mix 1 layer keeps and a v_mix 2 layer reads
   int64_t ld_keep = 0;
+  int q_only = 0;                // 1: the rows hold queries only (a layer that reads another layer's cached keys and values)
 };
 int launch_attn_prep(const AttnPrep& p, int dtype, cudaStream_t st);
 
@@ -33,6 +34,7 @@ int launch_attn_prep(const AttnPrep& p, int dtype, cudaStream_t st);
 constexpr int kScanMaxDim = 512;
 struct LinScan {
   int heads = 0, dk = 0, dv = 0, share = 1, d_scalar = 0;
+  int q_shared = 0;   // 1: q is [heads / share][dk] like b and r (the removal reads along a shared key)
   const float *d = nullptr, *p = nullptr, *q = nullptr, *b = nullptr, *r = nullptr, *v = nullptr, *vscale = nullptr;
   int64_t ld = 0;
   float* state = nullptr;
@@ -89,6 +91,30 @@ inline int64_t mamba_state_floats(int heads, int vdim, int state, int groups, in
   return (int64_t)heads * state * vdim + (int64_t)(taps - 1) * ((int64_t)heads * vdim + 2ll * groups * state);
 }
 int run_mamba(const MambaRun& p, int dtype, cudaStream_t st);
+
+// ---- gated delta rule around the scan: S ← g S − (beta·g·k)(kᵀS) + k (beta·v)ᵀ — the decayed state loses what it held
+// along the unit key and gains the new value there, both weighted by the write strength beta
+struct GatedDeltaRun {
+  b200_attn_desc a{};            // heads (value heads), kv_heads (query / key heads), dim, vdim
+  b200_gdelta_desc d{};
+  float eps = 1e-5f;
+  const void* proj = nullptr;    // [n_tok, ld_proj] T: q | k | v | out-gate logits | write strengths | decay logits
+  int64_t ld_proj = 0;
+  int off_q = 0, off_k = 0, off_v = 0, off_g = 0, off_b = 0, off_a = 0;
+  float* conv_state = nullptr;   // this run's [taps − 1][channels] fp32 of slot 0 (the slot stride is the scan's)
+  float* f = nullptr;            // [n_tok, gdelta_row_floats] fp32 workspace
+  LinScan scan{};
+  void* mid = nullptr;
+  int64_t ld_mid = 0;
+};
+inline int64_t gdelta_row_floats(int heads, int kv_heads, int dim, int vdim) {
+  return 2ll * heads + (int64_t)heads * dim + 2ll * kv_heads * dim + (int64_t)heads * vdim;
+}
+// floats of state per slot: S [heads][dim][vdim], then the convolutions' last taps − 1 inputs [taps − 1][channels]
+inline int64_t gdelta_state_floats(int heads, int kv_heads, int dim, int vdim, int taps) {
+  return (int64_t)heads * dim * vdim + (int64_t)(taps - 1) * (2ll * kv_heads * dim + (int64_t)heads * vdim);
+}
+int run_gdelta(const GatedDeltaRun& p, int dtype, cudaStream_t st);
 
 // x[r, :] += mult · rmsnorm(y[r, :]) · w  (fp32 stream), and h[r, :] = bf16(x[r, :]) — a sublayer's post-norm, the
 // residual sum and the next sublayer's operand copy in one pass; h may be null

@@ -17,7 +17,7 @@ from typing import Callable, Dict, Iterable, List, Optional, Tuple
 import torch
 
 from . import models
-from ._lib import (AttnDesc, AttnPrepDesc, B200Error, DeltaDesc, LatentDesc, LayerWeights, MambaDesc, MlstmDesc, ModelDesc,
+from ._lib import (AttnDesc, AttnPrepDesc, B200Error, DeltaDesc, GatedDeltaDesc, LatentDesc, LayerWeights, MambaDesc, MlstmDesc, ModelDesc,
                    MoeDesc, StackDesc, StackLayer, WeightTable, check, lib, require_device)
 
 
@@ -185,21 +185,46 @@ class DecodeEngine:
         self.slots = SequenceSlots(spec.max_slots)
 
     def _sandwich_layer(self, spec, i, L, ptr, mdt, acts) -> StackLayer:
-        """Descriptor of layer i of a sandwich-block model (latent attention or mLSTM mixer; dense or routed
-        feed-forward); the rotation tables are built here, for the engine's context length."""
+        """Descriptor of layer i of a sandwich-block model (latent attention, mLSTM, prepared attention or gated delta rule
+        mixer; dense or routed feed-forward); the rotation tables are built here, for the engine's context length."""
         lay, p = spec.mix_layout(i), f"l{i}."
         f32 = torch.float32
-        lat, rec, moe = LatentDesc(), MlstmDesc(), MoeDesc()
+        lat, rec, moe, prep, gdelta = LatentDesc(), MlstmDesc(), MoeDesc(), AttnPrepDesc(), GatedDeltaDesc()
+        kv_share = 0
+
+        def table(rot):
+            tab = self._rot_tables.get(rot)
+            if tab is None and rot is not None and rot.dims > 0:
+                tab = self._rot_tables[rot] = rot.table(spec.max_ctx).contiguous().to(self.device)
+            return tab
+
         if L.mixer == "latent_attention":
             a = L.latent
-            attn = AttnDesc(a.heads, 1, a.dim, a.vdim, a.scale, 0, 0, 0)
-            tab = self._rot_tables.get(a.rot)
-            if tab is None and a.rot.dims > 0:
-                tab = self._rot_tables[a.rot] = a.rot.table(spec.max_ctx).contiguous().to(self.device)
+            attn = AttnDesc(a.heads, 1, a.dim, a.vdim, a.scale, a.window, 0, 0)
+            tab = table(a.rot)
             lat = LatentDesc(a.kv_rank, a.rot_dim, a.rot.dims, ptr(p + "c_norm", f32), ptr(p + "uk_t", mdt), ptr(p + "uk", mdt),
                              ptr(p + "uv", mdt),
-                             tab.data_ptr() if tab is not None else None)
+                             tab.data_ptr() if tab is not None else None, int(a.rot_layout == "half"), a.q_rank,
+                             ptr(p + "q_norm", f32) if a.q_rank > 0 else None, ptr(p + "uq", mdt) if a.q_rank > 0 else None,
+                             int(a.out_gate))
             mixer = 1
+        elif L.mixer == "attention":
+            a, q = L.attn, L.prep or models.AttnPrepSpec()
+            attn = AttnDesc(a.heads, a.kv_heads, a.dim, a.vdim, a.scale, a.window, a.keep_first, int(a.out_gate), int(a.sink))
+            tab = table(q.rot)
+            if q.v_mix:
+                raise B200Error(f"DecodeEngine: layer {i}: the value mix-in is built for post-norm blocks")
+            prep = AttnPrepDesc(int(q.qk_norm), q.rot.dims if q.rot is not None else 0, int(q.v_norm), 0,
+                                ptr(p + "q_norm", f32) if q.qk_norm else None, ptr(p + "k_norm", f32) if q.qk_norm else None,
+                                tab.data_ptr() if tab is not None else None, None, int(q.rot_interleaved))
+            kv_share = 0 if L.kv_from is None else L.kv_from + 1
+            mixer = 0
+        elif L.mixer == "gated_delta":
+            a = L.gdelta
+            attn = AttnDesc(a.heads, a.kv_heads, a.dim, a.vdim, 1.0, 0, 0, 0)
+            gdelta = GatedDeltaDesc(a.conv, a.unit_eps, ptr(p + "conv_w", f32), ptr(p + "A_log", f32), ptr(p + "dt_bias", f32),
+                                    ptr(p + "head_norm", f32))
+            mixer = 5
         else:
             a = L.mlstm
             attn = AttnDesc(a.heads, a.heads, a.dim, a.vdim, 1.0, 0, 0, 0)
@@ -210,11 +235,12 @@ class DecodeEngine:
             m = L.moe
             moe = MoeDesc(m.experts, m.top, m.expert_ff, m.shared_ff, m.limit, m.shared_limit, ptr(p + "router", mdt),
                           ptr(p + "w_exp_in", mdt), ptr(p + "w_exp_out", mdt))
-        return StackLayer(attn, L.ff, acts[L.ff_act], lay.off_q, lay.off_k, lay.off_v, lay.off_g, lay.off_gate, 0, lay.n_in,
+        return StackLayer(attn, L.ff, acts[L.ff_act], lay.off_q, lay.off_k, lay.off_v, lay.off_g, lay.off_gate, lay.off_up, lay.n_in,
                           0, lay.k_out, ptr(p + "norm", f32), ptr(p + "w_in", mdt), ptr(p + "b_in", f32), ptr(p + "w_out", mdt),
                           0, None, None, None, mixer, 2 if L.ff_kind == "moe" else 1, ptr(p + "post_norm", f32),
                           ptr(p + "ff_norm", f32) if has_ff else None, ptr(p + "ff_post_norm", f32) if has_ff else None,
-                          ptr(p + "w_ff_in", mdt), ptr(p + "w_ff_out", mdt), lat, rec, moe)
+                          ptr(p + "w_ff_in", mdt), ptr(p + "w_ff_out", mdt), lat, rec, moe, prep, DeltaDesc(), MambaDesc(), gdelta,
+                          ptr(p + "b_out", f32), kv_share)
 
     def _postnorm_layer(self, spec, i, L, ptr, mdt, acts) -> StackLayer:
         """Descriptor of layer i of a post-norm-block model (prepared attention, generalized delta rule or Mamba-2 mixer;

@@ -195,6 +195,8 @@ class AttnSpec:
     keep_first: int = 0      # keys j < keep_first stay visible whatever the window
     out_gate: bool = True    # head output × sigmoid(gate logit)
     bias: bool = True        # q/k/v projections carry a bias
+    sink: bool = False       # the softmax's denominator gains 1 (a sink of score 0 that has no value)
+    out_bias: bool = False   # the out-projection carries a bias (sandwich blocks)
 
     def visible(self, i: int, j: int) -> bool:
         return j <= i and (self.window <= 0 or i - j < self.window or j < self.keep_first)
@@ -246,6 +248,10 @@ class LatentSpec:
     kv_rank: int
     scale: float
     rot: RotarySpec
+    rot_layout: str = "interleaved"   # interleaved: pairs (2i, 2i+1) | half: pairs (i, i + dims/2)
+    q_rank: int = 0          # > 0: queries go through an RMS-normed latent of this size (down- and up-projection)
+    window: int = 0          # key j visible from i when j <= i and i - j < window; 0 = every earlier key
+    out_gate: bool = False   # concatenated head outputs × sigmoid(gate projection of the layer input)
 
 
 @dataclass(frozen=True)
@@ -312,9 +318,10 @@ class AttnPrepSpec:
     and key projections, rotary positions, every value head divided by its root mean square, and the value mix-in (the
     first such layer of the model keeps its values, the later ones blend theirs with them by a learned weight)."""
     qk_norm: bool = False
-    rot: Optional[HalfRotarySpec] = None
+    rot: Optional[object] = None   # HalfRotarySpec (pairs i, i + dims/2), or a RotarySpec with rot_interleaved
     v_norm: bool = False
     v_mix: bool = False
+    rot_interleaved: bool = False  # pairs (2i, 2i+1)
 
 
 @dataclass(frozen=True)
@@ -349,11 +356,28 @@ class Mamba2Spec:
 
 
 @dataclass(frozen=True)
+class GatedDeltaSpec:
+    """Gated delta rule: `heads` value heads of `vdim`, `kv_heads` query / key heads of `dim` (value head h reads query / key
+    head h // (heads // kv_heads)); q, k, v pass causal convolutions of `conv` taps and SiLU; one decay and one write strength
+    per head; the state is a dim × vdim matrix per head."""
+    heads: int
+    kv_heads: int
+    dim: int
+    vdim: int
+    conv: int
+    unit_eps: float = 1e-6
+
+    @property
+    def channels(self) -> int:
+        return 2 * self.kv_heads * self.dim + self.heads * self.vdim
+
+
+@dataclass(frozen=True)
 class StackLayerSpec:
     attn: Optional[AttnSpec] = None  # mixer "attention"
     ff: int = 0                      # feed-forward width (gated / dense), 0 = none
     ff_act: str = "gelu_tanh"        # gelu_tanh | silu | gelu_erf
-    mixer: str = "attention"         # attention | latent_attention | mlstm | general_delta | mamba2
+    mixer: str = "attention"         # attention | latent_attention | mlstm | general_delta | mamba2 | gated_delta
     latent: Optional[LatentSpec] = None
     mlstm: Optional[MlstmSpec] = None
     ff_kind: str = "gated"           # gated | dense | moe
@@ -361,6 +385,8 @@ class StackLayerSpec:
     prep: Optional[AttnPrepSpec] = None   # attention mixers of sandwich / post-norm blocks
     delta: Optional[DeltaSpec] = None
     mamba: Optional[Mamba2Spec] = None
+    gdelta: Optional[GatedDeltaSpec] = None
+    kv_from: Optional[int] = None    # attention mixers: read the keys and values layer kv_from cached (no projections of its own)
 
 
 @dataclass(frozen=True)
@@ -420,6 +446,8 @@ class StackSpec:
     norm_kind: str = "rms"           # each sublayer | postnorm: a norm behind each sublayer only.  rms | layer (weight-only)
     loop_mix: bool = True            # every pass of the loop starts with x <- mix_in·[x; x0]
     logit_softcap: float = 0.0       # > 0: logits <- cap·tanh(logits / cap)
+    layer_scale: bool = False        # every sublayer's normed output is multiplied by a per-channel vector (the packer folds
+                                     # it into the post-norm's weight: both are element-wise factors of the same product)
 
     def runs(self) -> List[Tuple[int, bool]]:
         """(layer, mix the embedding in first) for every layer run, in execution order."""
@@ -447,8 +475,19 @@ class StackSpec:
         L = self.layers[i]
         if L.mixer == "latent_attention":
             a = L.latent
-            off_k = _up8(a.heads * (a.dim + a.rot_dim))
-            return MixLayout(off_q=0, off_k=off_k, n_in=off_k + _up8(a.kv_rank + a.rot_dim), k_out=a.heads * a.vdim)
+            off_k = _up8(a.q_rank if a.q_rank > 0 else a.heads * (a.dim + a.rot_dim))
+            off_g = off_k + _up8(a.kv_rank + a.rot_dim)
+            return MixLayout(off_q=0, off_k=off_k, off_g=off_g, n_in=off_g + (_up8(a.heads * a.vdim) if a.out_gate else 0),
+                             k_out=a.heads * a.vdim)
+        if L.mixer == "gated_delta":
+            a = L.gdelta
+            off_k = _up8(a.kv_heads * a.dim)
+            off_v = off_k + _up8(a.kv_heads * a.dim)
+            off_g = off_v + _up8(a.heads * a.vdim)
+            off_gate = off_g + _up8(a.heads * a.vdim)
+            off_up = off_gate + _up8(a.heads)
+            return MixLayout(off_q=0, off_k=off_k, off_v=off_v, off_g=off_g, off_gate=off_gate, off_up=off_up,
+                             n_in=off_up + _up8(a.heads), k_out=a.heads * a.vdim)
         if L.mixer == "mlstm":
             a = L.mlstm
             off_k = _up8(a.heads * a.dim)
@@ -456,6 +495,9 @@ class StackSpec:
             off_g = off_v + _up8(a.heads * a.vdim)
             off_gate = off_g + _up8(a.heads * a.vdim)
             return MixLayout(0, off_k, off_v, off_g, off_gate, off_gate + _up8(2 * a.heads), a.heads * a.vdim)
+        if L.mixer == "attention" and L.kv_from is not None:   # queries only
+            a = L.attn
+            return MixLayout(off_q=0, n_in=_up8(a.heads * a.dim), k_out=a.heads * a.vdim)
         if L.mixer == "attention":
             a = L.attn
             off_k = _up8(a.heads * a.dim)
@@ -486,8 +528,13 @@ class StackSpec:
             L, a = self.layers[i], self.layers[i].attn
             if L.mixer == "latent_attention":
                 q = L.latent
-                n += self.width * (q.heads * (q.dim + q.rot_dim) + q.kv_rank + q.rot_dim + q.heads * q.vdim)
-                n += q.heads * (q.dim + q.vdim) * q.kv_rank
+                hq = q.heads * (q.dim + q.rot_dim)
+                n += self.width * ((q.q_rank if q.q_rank > 0 else hq) + q.kv_rank + q.rot_dim + q.heads * q.vdim)
+                n += q.heads * (q.dim + q.vdim) * q.kv_rank + hq * q.q_rank
+                n += self.width * q.heads * q.vdim if q.out_gate else 0
+            elif L.mixer == "gated_delta":
+                q = L.gdelta
+                n += self.width * (2 * q.kv_heads * q.dim + 3 * q.heads * q.vdim + 2 * q.heads)
             elif L.mixer == "mlstm":
                 q = L.mlstm
                 n += self.width * (2 * q.heads * q.dim + 3 * q.heads * q.vdim + 2 * q.heads)
@@ -498,7 +545,7 @@ class StackSpec:
                 q = L.mamba
                 n += self.width * (2 * q.inner + 2 * q.groups * q.state + q.heads + q.inner)
             elif self.block != "parallel":
-                n += self.width * (a.heads * a.dim + a.kv_heads * (a.dim + a.vdim) + a.heads * a.vdim)
+                n += self.width * (a.heads * a.dim + (a.kv_heads * (a.dim + a.vdim) if L.kv_from is None else 0) + a.heads * a.vdim)
             if self.block != "parallel":
                 if L.ff_kind == "dense":
                     n += 2 * L.ff * self.width
@@ -976,6 +1023,223 @@ def pack_tekosun_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------- Tarudra
+def tarudra_from_config(doc: dict, name: str = "Tarudra") -> StackSpec:
+    """config.json of the Tarudra design → StackSpec.  Tarudra: sandwich blocks with weight-only layer norms and a per-channel
+    layer scale on every sublayer's normed output; mixers are a sliding-window attention (grouped heads, biases on q / k / v / o,
+    interleaved rotary pairs under YaRN stretching, a sink in the softmax's denominator; a layer may read the keys and
+    values an earlier layer cached), a latent attention (query latent, rotate-half rotary part, sliding window, element-wise
+    sigmoid output gate) or the gated delta rule behind short convolutions; dense squared-ReLU feed-forwards; tanh-capped logits."""
+    layers = []
+    for i, lc in enumerate(doc["layers"]):
+        kind, m = lc.get("type"), lc["mixer"]
+        window = int((m.get("mask") or {}).get("size", 0))
+        if kind == "attention":
+            heads, kv = int(m["heads"]), int(m["kv_heads"])
+            if kv < 1 or heads % kv:
+                raise ValueError(f"Tarudra: layer {i}: {heads} heads over {kv} kv_heads")
+            rot = _rotary_from_config(m["rot"]) if m.get("rot") else None
+            if rot is not None and (rot.dims % 2 or rot.dims > int(m["dim"])):
+                raise ValueError(f"Tarudra: layer {i}: rot.dims {rot.dims} must be even and at most dim")
+            if rot is not None and rot.dims == 0:
+                rot = None
+            attn = AttnSpec(heads=heads, kv_heads=kv, dim=int(m["dim"]), vdim=int(m["vdim"]), scale=float(m["scale"]),
+                            window=window, keep_first=0, out_gate=False, bias=True, sink=True, out_bias=True)
+            src = m.get("kv_from")
+            if src is not None:
+                src = int(src)
+                S = layers[src] if 0 <= src < i else None
+                if S is None or S.mixer != "attention" or S.kv_from is not None:
+                    raise ValueError(f"Tarudra: layer {i}: kv_from {src} is not an earlier attention layer with keys and values of its own")
+                if (S.attn.kv_heads, S.attn.dim, S.attn.vdim) != (kv, attn.dim, attn.vdim):
+                    raise ValueError(f"Tarudra: layer {i}: the keys and values of layer {src} have other sizes")
+            kw = dict(mixer="attention", attn=attn, kv_from=src,
+                      prep=AttnPrepSpec(qk_norm=False, rot=rot, v_norm=False, v_mix=False, rot_interleaved=True))
+        elif kind == "latent_attention":
+            rot = _rotary_from_config(m["rot"]) if m.get("rot") and int(m["rot_dim"]) > 0 else RotarySpec(dims=0, base=10000.0)
+            if rot.dims % 2 or rot.dims > int(m["rot_dim"]):
+                raise ValueError(f"Tarudra: layer {i}: rot.dims {rot.dims} must be even and at most rot_dim")
+            kw = dict(mixer=kind, latent=LatentSpec(heads=int(m["heads"]), dim=int(m["dim"]), rot_dim=int(m["rot_dim"]),
+                                                    vdim=int(m["vdim"]), kv_rank=int(m["kv_rank"]), scale=float(m["scale"]),
+                                                    rot=rot, rot_layout="half", q_rank=int(m["q_rank"]), window=window,
+                                                    out_gate=True))
+            if kw["latent"].q_rank < 1:
+                raise ValueError(f"Tarudra: layer {i}: q_rank {kw['latent'].q_rank}")
+        elif kind == "delta":
+            heads, kv = int(m["heads"]), int(m["kv_heads"])
+            if kv < 1 or heads % kv or int(m["conv"]) < 1:
+                raise ValueError(f"Tarudra: layer {i}: {heads} heads over {kv} kv_heads, {m['conv']} taps")
+            kw = dict(mixer="gated_delta", gdelta=GatedDeltaSpec(heads=heads, kv_heads=kv, dim=int(m["dim"]), vdim=int(m["vdim"]),
+                                                                 conv=int(m["conv"])))
+        else:
+            raise ValueError(f"Tarudra: layer {i}: mixer type {kind!r} is not part of the design")
+        mlp = lc.get("mlp")
+        if mlp is None:
+            kw.update(ff_kind="dense", ff=0, ff_act="relu2")
+        elif mlp.get("kind") == "dense":
+            kw.update(ff_kind="dense", ff=int(mlp["ff"]), ff_act="relu2")
+        else:
+            raise ValueError(f"Tarudra: layer {i}: feed-forward kind {mlp.get('kind')!r} is not part of the design")
+        layers.append(StackLayerSpec(**kw))
+    return StackSpec(name=name, architecture="Tarudra", width=int(doc["width"]), vocab=int(doc["vocab"]), layers=tuple(layers),
+                     norm_eps=float(doc["norm"]["eps"]), norm_offset=0.0, block="sandwich", norm_kind="layer", loop_mix=False,
+                     logit_softcap=float(doc.get("logit_softcap") or 0.0), layer_scale=True)
+
+
+def _rotary_config(r: RotarySpec) -> dict:
+    rot = {"base": r.base, "dims": r.dims}
+    if r.factor > 0:
+        rot["scaling"] = {"factor": r.factor, "fast": r.fast, "original": r.original, "slow": r.slow}
+    return rot
+
+
+def tarudra_config(spec: StackSpec) -> dict:
+    """The config.json a Tarudra StackSpec is read from (inverse of tarudra_from_config)."""
+    doc = {"architecture": "Tarudra", "layers": [], "logit_softcap": spec.logit_softcap, "norm": {"eps": spec.norm_eps},
+           "vocab": spec.vocab, "width": spec.width}
+    kinds = {"attention": "attention", "latent_attention": "latent_attention", "gated_delta": "delta"}
+    for L in spec.layers:
+        if L.mixer == "attention":
+            a = L.attn
+            mixer = {"dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "scale": a.scale, "vdim": a.vdim}
+            if a.window > 0:
+                mixer["mask"] = {"size": a.window}
+            if L.prep.rot is not None:
+                mixer["rot"] = _rotary_config(L.prep.rot)
+            if L.kv_from is not None:
+                mixer["kv_from"] = L.kv_from
+        elif L.mixer == "latent_attention":
+            a = L.latent
+            mixer = {"dim": a.dim, "heads": a.heads, "kv_rank": a.kv_rank, "q_rank": a.q_rank, "rot_dim": a.rot_dim,
+                     "scale": a.scale, "vdim": a.vdim}
+            if a.window > 0:
+                mixer["mask"] = {"size": a.window}
+            if a.rot_dim > 0:
+                mixer["rot"] = _rotary_config(a.rot)
+        else:
+            a = L.gdelta
+            mixer = {"conv": a.conv, "dim": a.dim, "heads": a.heads, "kv_heads": a.kv_heads, "vdim": a.vdim}
+        doc["layers"].append({"mixer": mixer, "mlp": {"ff": L.ff, "kind": "dense"} if L.ff > 0 else None, "type": kinds[L.mixer]})
+    return doc
+
+
+def tarudra_tensor_shapes(spec: StackSpec) -> Dict[str, Tuple[int, ...]]:
+    """Checkpoint tensor names and shapes of a Tarudra model (Linear weights are [out, in])."""
+    W, out = spec.width, {}
+    out["embed"] = (spec.vocab, W)
+    for i, L in enumerate(spec.layers):
+        p = f"l{i}."
+        out[p + "norm1"], out[p + "norm1b"], out[p + "ls1"] = (W,), (W,), (W,)
+        if L.mixer == "attention":
+            a = L.attn
+            segs = [("q", a.heads * a.dim)] + ([("k", a.kv_heads * a.dim), ("v", a.kv_heads * a.vdim)] if L.kv_from is None else [])
+            for nm, rows in segs:
+                out[p + "mix." + nm], out[p + "mix." + nm + ".b"] = (rows, W), (rows,)
+            out[p + "mix.o"], out[p + "mix.o.b"] = (W, a.heads * a.vdim), (W,)
+        elif L.mixer == "latent_attention":
+            a = L.latent
+            out[p + "mix.dq"], out[p + "mix.dq.norm"] = (a.q_rank, W), (a.q_rank,)
+            out[p + "mix.uq"] = (a.heads * (a.dim + a.rot_dim), a.q_rank)
+            out[p + "mix.dkv"], out[p + "mix.dkv.norm"] = (a.kv_rank + a.rot_dim, W), (a.kv_rank,)
+            out[p + "mix.uk"], out[p + "mix.uv"] = (a.heads * a.dim, a.kv_rank), (a.heads * a.vdim, a.kv_rank)
+            out[p + "mix.g"], out[p + "mix.o"] = (a.heads * a.vdim, W), (W, a.heads * a.vdim)
+        else:
+            a = L.gdelta
+            for nm, rows in (("q", a.kv_heads * a.dim), ("k", a.kv_heads * a.dim), ("v", a.heads * a.vdim)):
+                out[p + "mix." + nm], out[p + "mix." + nm + ".conv"] = (rows, W), (rows, a.conv)
+            out[p + "mix.b"], out[p + "mix.a"] = (a.heads, W), (a.heads, W)
+            out[p + "mix.A_log"], out[p + "mix.dt_bias"], out[p + "mix.norm"] = (a.heads,), (a.heads,), (a.vdim,)
+            out[p + "mix.g"], out[p + "mix.o"] = (a.heads * a.vdim, W), (W, a.heads * a.vdim)
+        if L.ff > 0:
+            out[p + "norm2"], out[p + "norm2b"], out[p + "ls2"] = (W,), (W,), (W,)
+            out[p + "mlp.up"], out[p + "mlp.down"] = (L.ff, W), (W, L.ff)
+    out["final.norm"] = (W,)
+    out["head"] = (spec.vocab, W)
+    return out
+
+
+def synth_tarudra_weights(spec: StackSpec, seed: int = 0, std: float = 0.05) -> Dict[str, torch.Tensor]:
+    """Seeded synthetic Tarudra checkpoint (bf16, checkpoint names): matrices N(0, std·√(64/in)), norm weights 1 + N(0, 0.1),
+    layer scales in (0.3, 1.0), biases N(0, 0.5), convolution taps N(0, 0.5), decays and write strengths in the range where
+    the state both keeps and forgets."""
+    g = torch.Generator().manual_seed(seed)
+    w = {}
+    for name, shape in tarudra_tensor_shapes(spec).items():
+        t = torch.randn(shape, generator=g)
+        if name.endswith("ls1") or name.endswith("ls2"):
+            t = 0.65 + 0.35 * torch.tanh(t)
+        elif name.endswith("A_log"):
+            t = 0.5 * t
+        elif name.endswith("dt_bias"):
+            t = t - 1.0
+        elif name.endswith(".conv") or name.endswith(".b") and len(shape) == 1:
+            t = t * 0.5
+        elif len(shape) == 1:
+            t = 1.0 + 0.1 * t
+        else:
+            t = t * (std * (64.0 / shape[1]) ** 0.5)
+        w[name] = t.to(torch.bfloat16)
+    return w
+
+
+def pack_tarudra_weights(spec: StackSpec, named: Dict[str, torch.Tensor], device="cuda",
+                         dtype: torch.dtype = torch.bfloat16) -> Dict[str, torch.Tensor]:
+    """Checkpoint tensors (Tarudra names) → the engine's layout on `device`.  Per layer: w_in = the mixer's in-projections merged
+    by rows (StackSpec.mix_layout) with their biases in the fp32 b_in, w_out = mix.o (+ b_out); the layer scale is folded into the
+    post-norm's weight (the product of two bf16 values is exact in fp32); latent attention: the query's up-projection with its
+    columns padded to 8, uk both as stored and transposed per head; gated delta rule: the three convolutions' taps as one fp32
+    [channels, taps] block in q | k | v order.  Vectors in fp32, matrices in `dtype`."""
+    W = spec.width
+    out: Dict[str, torch.Tensor] = {}
+
+    def mat(t):
+        return t.to(dtype).contiguous().to(device)
+
+    def vec(t):
+        return t.to(torch.float32).reshape(-1).contiguous().to(device)
+
+    out["embed"], out["head"], out["final_norm"] = mat(named["embed"]), mat(named["head"]), vec(named["final.norm"])
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.mix_layout(i), f"l{i}."
+        w_in = torch.zeros(lay.n_in, W, dtype=dtype)
+        b_in = torch.zeros(lay.n_in, dtype=torch.float32)
+
+        def put(off, name, bias=None):
+            t = named[p + name]
+            w_in[off:off + t.shape[0]] = t.to(dtype)
+            if bias is not None:
+                b_in[off:off + t.shape[0]] = named[p + bias].to(torch.float32)
+
+        if L.mixer == "attention":
+            put(lay.off_q, "mix.q", "mix.q.b")
+            if L.kv_from is None:
+                put(lay.off_k, "mix.k", "mix.k.b"), put(lay.off_v, "mix.v", "mix.v.b")
+            out[p + "b_in"], out[p + "b_out"] = b_in.to(device), vec(named[p + "mix.o.b"])
+        elif L.mixer == "latent_attention":
+            a = L.latent
+            put(lay.off_q, "mix.dq"), put(lay.off_k, "mix.dkv"), put(lay.off_g, "mix.g")
+            uq = torch.zeros(a.heads * (a.dim + a.rot_dim), _up8(a.q_rank), dtype=dtype)
+            uq[:, :a.q_rank] = named[p + "mix.uq"].to(dtype)
+            out[p + "uq"], out[p + "q_norm"] = uq.to(device), vec(named[p + "mix.dq.norm"])
+            out[p + "c_norm"] = vec(named[p + "mix.dkv.norm"])
+            out[p + "uk_t"] = mat(named[p + "mix.uk"].view(a.heads, a.dim, a.kv_rank).transpose(1, 2))
+            out[p + "uk"], out[p + "uv"] = mat(named[p + "mix.uk"]), mat(named[p + "mix.uv"])
+        else:
+            put(lay.off_q, "mix.q"), put(lay.off_k, "mix.k"), put(lay.off_v, "mix.v"), put(lay.off_g, "mix.g")
+            put(lay.off_gate, "mix.b"), put(lay.off_up, "mix.a")
+            out[p + "conv_w"] = vec(torch.cat([named[p + "mix.q.conv"], named[p + "mix.k.conv"], named[p + "mix.v.conv"]], 0))
+            out[p + "A_log"], out[p + "dt_bias"] = vec(named[p + "mix.A_log"]), vec(named[p + "mix.dt_bias"])
+            out[p + "head_norm"] = vec(named[p + "mix.norm"])
+        out[p + "w_in"], out[p + "w_out"] = w_in.to(device), mat(named[p + "mix.o"])
+        out[p + "norm"] = vec(named[p + "norm1"])
+        out[p + "post_norm"] = vec(named[p + "norm1b"].to(torch.float32) * named[p + "ls1"].to(torch.float32))
+        if L.ff > 0:
+            out[p + "ff_norm"] = vec(named[p + "norm2"])
+            out[p + "ff_post_norm"] = vec(named[p + "norm2b"].to(torch.float32) * named[p + "ls2"].to(torch.float32))
+            out[p + "w_ff_in"], out[p + "w_ff_out"] = mat(named[p + "mlp.up"]), mat(named[p + "mlp.down"])
+    return out
+
+
 @dataclass(frozen=True)
 class Architecture:
     """One design of the layer-stack registry: its config reader and writer, checkpoint tensor list, synthetic checkpoint
@@ -1133,6 +1397,8 @@ ARCHITECTURES["Silatar"] = Architecture(silatar_from_config, silatar_config, sil
                                         pack_silatar_weights)
 ARCHITECTURES["Tekosun"] = Architecture(tekosun_from_config, tekosun_config, tekosun_tensor_shapes, synth_tekosun_weights,
                                         pack_tekosun_weights, with_shapes=True)
+ARCHITECTURES["Tarudra"] = Architecture(tarudra_from_config, tarudra_config, tarudra_tensor_shapes, synth_tarudra_weights,
+                                        pack_tarudra_weights)
 
 
 # ------------------------------------------------------------------------------------------- checkpoint writer
