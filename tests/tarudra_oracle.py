@@ -88,9 +88,9 @@ def attention_keys_values(h: torch.Tensor, positions: torch.Tensor, m: dict, w: 
 
 
 def attention(h: torch.Tensor, positions: torch.Tensor, m: dict, w: Dict[str, torch.Tensor], p: str, keys: torch.Tensor,
-              values: torch.Tensor, key_positions: torch.Tensor) -> torch.Tensor:
+              values: torch.Tensor, key_positions: torch.Tensor, sink: bool = True) -> torch.Tensor:
     """Windowed attention of the rows h over (keys, values) at key_positions; the softmax has a sink: 1 is added to its
-    denominator."""
+    denominator (sink=False: an ordinary softmax, for tests that show the sink matters)."""
     T, H, G, dk, dv = h.shape[0], int(m["heads"]), int(m["kv_heads"]), int(m["dim"]), int(m["vdim"])
     q = (h @ w[p + "mix.q"].T + w[p + "mix.q.b"]).view(T, H, dk)
     if m.get("rot"):
@@ -103,7 +103,7 @@ def attention(h: torch.Tensor, positions: torch.Tensor, m: dict, w: Dict[str, to
         s = s.masked_fill(~vis, float("-inf"))
         mx = s.max(-1, keepdim=True).values.clamp_min(0.0)
         e = torch.exp(s - mx)
-        out[:, hd] = (e / (torch.exp(-mx) + e.sum(-1, keepdim=True))) @ values[:, g]
+        out[:, hd] = (e / ((torch.exp(-mx) if sink else 0.0) + e.sum(-1, keepdim=True))) @ values[:, g]
     return out.reshape(T, H * dv) @ w[p + "mix.o"].T + w[p + "mix.o.b"]
 
 
@@ -194,7 +194,8 @@ class Sequence:
         self.mem: List[dict] = [{} for _ in cfg["layers"]]
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, seq: Optional[Sequence] = None, layer_outputs: Optional[list] = None):
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, seq: Optional[Sequence] = None, layer_outputs: Optional[list] = None,
+            sink: bool = True):
     """Logits [T, vocab] of the new tokens of one sequence; `seq` carries the memory of the earlier ones."""
     seq = seq if seq is not None else Sequence(cfg)
     eps = float(cfg["norm"]["eps"])
@@ -213,7 +214,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, seq: Optional[Sequenc
                 mem["v"] = torch.cat([mem["v"], v], 0) if "v" in mem else v
                 src = i
             keys, values = seq.mem[int(src)]["k"], seq.mem[int(src)]["v"]
-            y = attention(h, positions, m, w, p, keys, values, torch.arange(keys.shape[0]))
+            y = attention(h, positions, m, w, p, keys, values, torch.arange(keys.shape[0]), sink=sink)
         elif lc["type"] == "latent_attention":
             c, kr = latent_cache_rows(h, positions, m, w, p, eps)
             mem["c"] = torch.cat([mem["c"], c], 0) if "c" in mem else c

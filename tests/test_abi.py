@@ -62,13 +62,15 @@ def test_stack_struct_layouts_match_the_compiler(built_lib, tmp_path):
     from tinygpt_b200 import _lib
     src = tmp_path / "sz.c"
     src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "b200_decode.h"\n'
-                   'int main(void) { printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(b200_attn_desc), '
+                   'int main(void) { printf("%zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu %zu\\n", sizeof(b200_attn_desc), '
                    'sizeof(b200_stack_layer), sizeof(b200_stack_desc), offsetof(b200_stack_layer, side_norm), '
                    'offsetof(b200_stack_desc, layers_host), offsetof(b200_stack_layer, w_out), sizeof(b200_latent_desc), '
                    'sizeof(b200_mlstm_desc), sizeof(b200_moe_desc), offsetof(b200_stack_layer, moe), '
                    'offsetof(b200_stack_layer, lat), offsetof(b200_stack_desc, logit_softcap), sizeof(b200_attn_prep_desc), '
                    'sizeof(b200_delta_desc), sizeof(b200_mamba_desc), offsetof(b200_stack_layer, mamba), '
-                   'offsetof(b200_moe_desc, route_scale)); return 0; }\n')
+                   'offsetof(b200_moe_desc, route_scale), sizeof(b200_gdelta_desc), offsetof(b200_stack_layer, gdelta), '
+                   'offsetof(b200_stack_layer, kv_share), offsetof(b200_latent_desc, out_gate), '
+                   'offsetof(b200_attn_prep_desc, rot_interleaved)); return 0; }\n')
     exe = tmp_path / "sz"
     subprocess.run(["gcc", "-I", str(ROOT / "include"), str(src), "-o", str(exe)], check=True)
     got = [int(v) for v in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
@@ -76,7 +78,9 @@ def test_stack_struct_layouts_match_the_compiler(built_lib, tmp_path):
             _lib.StackDesc.layers_host.offset, _lib.StackLayer.w_out.offset, C.sizeof(_lib.LatentDesc),
             C.sizeof(_lib.MlstmDesc), C.sizeof(_lib.MoeDesc), _lib.StackLayer.moe.offset, _lib.StackLayer.lat.offset,
             _lib.StackDesc.logit_softcap.offset, C.sizeof(_lib.AttnPrepDesc), C.sizeof(_lib.DeltaDesc), C.sizeof(_lib.MambaDesc),
-            _lib.StackLayer.mamba.offset, _lib.MoeDesc.route_scale.offset]
+            _lib.StackLayer.mamba.offset, _lib.MoeDesc.route_scale.offset, C.sizeof(_lib.GatedDeltaDesc),
+            _lib.StackLayer.gdelta.offset, _lib.StackLayer.kv_share.offset, _lib.LatentDesc.out_gate.offset,
+            _lib.AttnPrepDesc.rot_interleaved.offset]
     assert got == want
 
 
