@@ -685,7 +685,17 @@ def main():
                     help="instead of the headline run: prefill / decode throughput of the Tekosun layer-stack design (delta rule, "
                          "Mamba-2, prepared windowed attention, softmax-routed experts) beside the Silatar design of equal width, "
                          "vocabulary and layer runs (sizes of tinygpt_b200/stack_bench.py, or all)")
+    ap.add_argument("--tarudra-compare", nargs="?", const="all", default=None, metavar="SIZES",
+                    help="instead of the headline run: prefill / decode throughput of the Tarudra layer-stack design (sink attention "
+                         "with shared keys / values, latent attention with a query latent, gated delta rule, dense feed-forwards) "
+                         "beside the Silatar design with dense feed-forwards of equal width, vocabulary and layer runs (sizes of "
+                         "tinygpt_b200/stack_bench.py, or all)")
     args = ap.parse_args()
+    if args.tarudra_compare is not None:
+        from tinygpt_b200 import build, stack_bench
+        build.build()
+        stack_bench.main_tarudra(args.tarudra_compare, steps=max(1, min(args.steps, 10)), warmup=max(3, args.warmup))
+        return
     if args.tekosun_compare is not None:
         from tinygpt_b200 import build, stack_bench
         build.build()

@@ -408,26 +408,29 @@ __device__ __forceinline__ int gdelta_col(const GatedDeltaRun& p, int c, int nqk
   return c < nqk ? p.off_q + c : c < 2 * nqk ? p.off_k + (c - nqk) : p.off_v + (c - 2 * nqk);
 }
 
-// One CTA per token.  First every channel of q | k | v: the short causal convolution over the row's own input and the
-// taps − 1 before it (rows of the same sequence in this step, else the slot's state; zeros before position 0), then SiLU,
-// into shared memory.  Then one warp per head: q and k heads become unit vectors (q also times dim^(−1/2)); value heads get
-// their write strength beta = sigmoid(·) and decay g = exp(−exp(A_log)·softplus(· + dt_bias)).  The scan's fp32 rows:
+// One CTA per (token, query / key head g): the channels of q head g, k head g and the value heads that read them.  First the
+// short causal convolution of every such channel over the row's own input and the taps − 1 before it (rows of the same
+// sequence in this step, else the slot's state; zeros before position 0), then SiLU, into shared memory.  Then q and k
+// become unit vectors (q also times dim^(−1/2)), and one warp per value head: its write strength beta = sigmoid(·), its decay
+// g = exp(−exp(A_log)·softplus(· + dt_bias)).  The scan's fp32 rows:
 //   [g: H | beta·g·k (the removal's weight vector): H·dk | k: G·dk | q: G·dk | v: H·dv | beta: H]
 // The state is only READ here (gdelta_out_kernel, a later launch, moves it on).
 template <typename T>
 __global__ void __launch_bounds__(256) gdelta_prep_kernel(const GatedDeltaRun p) {
   pdl_trigger();
   pdl_wait();
-  extern __shared__ float sm[];   // [2·G·dk + H·dv] convolved channels
-  const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int H = p.a.heads, G = p.a.kv_heads, dk = p.a.dim, dv = p.a.vdim, taps = p.d.taps;
-  const int nqk = G * dk, ch = 2 * nqk + H * dv;
+  extern __shared__ float sm[];   // [dk: q | dk: k | per·dv: v] convolved channels of this group
+  const int t = blockIdx.x, g = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int H = p.a.heads, G = p.a.kv_heads, dk = p.a.dim, dv = p.a.vdim, taps = p.d.taps, per = H / G;
+  const int nqk = G * dk, ch = 2 * nqk + H * dv, mine = 2 * dk + per * dv;
   const int32_t *slot = p.scan.slot, *pos = p.scan.pos;
   const T* proj = static_cast<const T*>(p.proj);
   const float* cs = p.conv_state + (int64_t)slot[t] * p.scan.slot_stride;
   int in_step = 0;   // rows of this sequence in front of row t, counted up to taps − 1
   while (in_step < taps - 1 && same_seq(slot, pos, t, in_step + 1)) ++in_step;
-  for (int c = tid; c < ch; c += 256) {
+  for (int e = tid; e < mine; e += 256) {
+    // the group's e-th channel → its place c among the q | k | v channels
+    const int c = e < dk ? g * dk + e : e < 2 * dk ? nqk + g * dk + (e - dk) : 2 * nqk + g * per * dv + (e - 2 * dk);
     const int col = gdelta_col(p, c, nqk);
     float acc = 0.f;
     for (int j = 0; j < taps; ++j) {   // j positions back; weight column taps − 1 − j
@@ -436,7 +439,7 @@ __global__ void __launch_bounds__(256) gdelta_prep_kernel(const GatedDeltaRun p)
       else if (pos[t] - j >= 0) v = cs[(int64_t)(taps - 1 - (j - in_step)) * ch + c];
       acc = fmaf(p.d.conv_w[(int64_t)c * taps + taps - 1 - j], v, acc);
     }
-    sm[c] = siluf(acc);
+    sm[e] = siluf(acc);
   }
   __syncthreads();
   float* f = p.f + (int64_t)t * p.scan.ld;
@@ -446,28 +449,32 @@ __global__ void __launch_bounds__(256) gdelta_prep_kernel(const GatedDeltaRun p)
   float* f_q = f_k + nqk;
   float* f_v = f_q + nqk;
   float* f_beta = f_v + (int64_t)H * dv;
-  // unit query / key heads
-  for (int u = warp; u < 2 * G; u += 8) {
-    const float* x = sm + (int64_t)u * dk;   // q heads first, then k heads
+  if (warp < 2) {   // warp 0: the unit query, warp 1: the unit key (kept in shared memory for the value heads)
+    float* x = sm + warp * dk;
     float ss = 0.f;
     for (int i = lane; i < dk; i += 32) ss += x[i] * x[i];
     float inv = 1.f / sqrtf(warp_sum(ss) + p.d.unit_eps);
-    if (u < G) inv *= rsqrtf((float)dk);
-    float* dst = u < G ? f_q + (int64_t)u * dk : f_k + (int64_t)(u - G) * dk;
-    for (int i = lane; i < dk; i += 32) dst[i] = x[i] * inv;
+    if (warp == 0) inv *= rsqrtf((float)dk);
+    float* dst = (warp == 0 ? f_q : f_k) + (int64_t)g * dk;
+    for (int i = lane; i < dk; i += 32) {
+      const float u = x[i] * inv;
+      x[i] = u;
+      dst[i] = u;
+    }
   }
-  __syncthreads();   // f_k of this row is read below
+  __syncthreads();
   const T* row = proj + (int64_t)t * p.ld_proj;
-  for (int hd = warp; hd < H; hd += 8) {
+  const float* k = sm + dk;
+  for (int u = warp; u < per; u += 8) {
+    const int hd = g * per + u;
     const float beta = sigmoidf(ldf<T>(row + p.off_b + hd));
-    const float g = expf(-expf(p.d.A_log[hd]) * softplusf(ldf<T>(row + p.off_a + hd) + p.d.dt_bias[hd]));
+    const float dec = expf(-expf(p.d.A_log[hd]) * softplusf(ldf<T>(row + p.off_a + hd) + p.d.dt_bias[hd]));
     if (lane == 0) {
-      f_g[hd] = g;
+      f_g[hd] = dec;
       f_beta[hd] = beta;
     }
-    const float* k = f_k + (int64_t)(hd / (H / G)) * dk;
-    for (int i = lane; i < dk; i += 32) f_p[(int64_t)hd * dk + i] = beta * g * k[i];
-    for (int i = lane; i < dv; i += 32) f_v[(int64_t)hd * dv + i] = sm[2 * nqk + hd * dv + i];
+    for (int i = lane; i < dk; i += 32) f_p[(int64_t)hd * dk + i] = beta * dec * k[i];
+    for (int i = lane; i < dv; i += 32) f_v[(int64_t)hd * dv + i] = sm[2 * dk + u * dv + i];
   }
 }
 
@@ -643,8 +650,8 @@ int run_gdelta(const GatedDeltaRun& p, int dtype, cudaStream_t st) {
   B200_CHECK_ARG(p.d.taps >= 1 && p.d.taps <= kMambaMaxTaps, "gated delta rule: 1 … %d convolution taps", kMambaMaxTaps);
   B200_CHECK_ARG(p.d.conv_w && p.d.A_log && p.d.dt_bias && p.d.head_norm && p.d.unit_eps >= 0.f, "gated delta rule: null weight");
   const int nqk = G * dk, ch = 2 * nqk + H * dv;
-  const size_t smem = (size_t)ch * 4;
-  B200_CHECK_ARG(smem <= 200 * 1024, "gated delta rule: %d convolved channels exceed one CTA's shared memory", ch);
+  const size_t smem = (size_t)(2 * dk + (H / G) * dv) * 4;
+  B200_CHECK_ARG(smem <= 200 * 1024, "gated delta rule: the channels of one query / key head and its value heads exceed one CTA's shared memory");
   if (smem > 48 * 1024) {
     static bool attr_done = false;
     if (!attr_done) {
@@ -653,8 +660,9 @@ int run_gdelta(const GatedDeltaRun& p, int dtype, cudaStream_t st) {
       attr_done = true;
     }
   }
-  if (dtype == B200_F32) B200_CUDA(launch_pdl(gdelta_prep_kernel<float>, dim3(p.scan.n_tok), dim3(256), smem, st, stack_pdl(), p));
-  else B200_CUDA(launch_pdl(gdelta_prep_kernel<__nv_bfloat16>, dim3(p.scan.n_tok), dim3(256), smem, st, stack_pdl(), p));
+  const dim3 pg(p.scan.n_tok, G);
+  if (dtype == B200_F32) B200_CUDA(launch_pdl(gdelta_prep_kernel<float>, pg, dim3(256), smem, st, stack_pdl(), p));
+  else B200_CUDA(launch_pdl(gdelta_prep_kernel<__nv_bfloat16>, pg, dim3(256), smem, st, stack_pdl(), p));
   LinScan s = p.scan;
   s.heads = H; s.dk = dk; s.dv = dv; s.share = H / G; s.d_scalar = 1; s.q_shared = 1;
   s.d = p.f; s.p = p.f + H; s.q = s.p + (int64_t)H * dk; s.b = s.q; s.r = s.q + nqk; s.v = s.r + nqk;

@@ -272,6 +272,117 @@ def main_tekosun(sizes: str, steps: int, warmup: int) -> None:
     print(json.dumps(compare_tekosun(names, steps=steps, warmup=warmup)), flush=True)
 
 
+# Tarudra sizes: eight layers [latent, latent, gated delta rule, attention, latent, latent, gated delta rule, attention reading
+# the first attention layer's keys and values], every one with a dense squared-ReLU feed-forward.  The model beside it is
+# the Silatar design — the framework's other sandwich-block design with layer norms, a latent attention, a recurrent mixer and
+# capped logits — with dense feed-forwards of the same width, the same latent sizes in every attention place and its mLSTM (a
+# matrix memory of the same number of floats as the delta rule's) in the recurrent places.
+TARUDRA_SIZES = {
+    "r2048": dict(width=2048, vocab=65536, heads=16, kv_heads=8, dim=128, window=1024, rot_dims=64, l_heads=16, l_dim=64, l_rot=64,
+                  l_vdim=128, kv_rank=512, q_rank=768, d_heads=16, d_kv=8, d_dim=128, d_vdim=128, conv=4, ff=8192,
+                  rec_heads=8, rec_dim=128, rec_vdim=256),
+    "r3072": dict(width=3072, vocab=65536, heads=24, kv_heads=8, dim=128, window=1024, rot_dims=64, l_heads=24, l_dim=64, l_rot=64,
+                  l_vdim=128, kv_rank=512, q_rank=1536, d_heads=24, d_kv=8, d_dim=128, d_vdim=128, conv=4, ff=12288,
+                  rec_heads=8, rec_dim=192, rec_vdim=384),
+}
+
+
+def tarudra_spec(name: str, max_ctx: int, max_slots: int = 8) -> models.StackSpec:
+    z = TARUDRA_SIZES[name]
+    yarn = models.RotarySpec(dims=z["rot_dims"], base=1e4, factor=2.0, original=1024, fast=32.0, slow=1.0)
+    attn = models.AttnSpec(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["dim"] ** -0.5, z["window"], 0, out_gate=False, bias=True,
+                           sink=True, out_bias=True)
+    prep = models.AttnPrepSpec(rot=yarn, rot_interleaved=True)
+    lat = models.LatentSpec(z["l_heads"], z["l_dim"], z["l_rot"], z["l_vdim"], z["kv_rank"], (z["l_dim"] + z["l_rot"]) ** -0.5,
+                            models.RotarySpec(dims=z["l_rot"], base=5e5), rot_layout="half", q_rank=z["q_rank"], window=z["window"],
+                            out_gate=True)
+    gd = models.GatedDeltaSpec(z["d_heads"], z["d_kv"], z["d_dim"], z["d_vdim"], z["conv"])
+    L = models.StackLayerSpec
+    kw = dict(ff_kind="dense", ff=z["ff"], ff_act="relu2")
+    l, d = L(mixer="latent_attention", latent=lat, **kw), L(mixer="gated_delta", gdelta=gd, **kw)
+    a, a2 = L(mixer="attention", attn=attn, prep=prep, **kw), L(mixer="attention", attn=attn, prep=prep, kv_from=3, **kw)
+    return models.StackSpec(name="tarudra-" + name, architecture="Tarudra", width=z["width"], vocab=z["vocab"],
+                            layers=(l, l, d, a, l, l, d, a2), norm_eps=1e-6, block="sandwich", norm_kind="layer", loop_mix=False,
+                            logit_softcap=15.0, layer_scale=True, max_ctx=max_ctx, max_slots=max_slots)
+
+
+def silatar_dense_beside(name: str, max_ctx: int, max_slots: int = 8) -> models.StackSpec:
+    z = TARUDRA_SIZES[name]
+    rot = models.RotarySpec(dims=z["l_rot"], base=5e5, factor=4.0, original=2048, fast=32.0, slow=1.0)
+    lat = models.LatentSpec(z["l_heads"], z["l_dim"], z["l_rot"], z["l_vdim"], z["kv_rank"], (z["l_dim"] + z["l_rot"]) ** -0.5, rot)
+    rec = models.MlstmSpec(z["rec_heads"], z["rec_dim"], z["rec_vdim"], 15.0)
+    L = models.StackLayerSpec
+    kw = dict(ff_kind="dense", ff=z["ff"], ff_act="gelu_erf")
+    l, r = L(mixer="latent_attention", latent=lat, **kw), L(mixer="mlstm", mlstm=rec, **kw)
+    return models.StackSpec(name="silatar-dense-" + name, architecture="Silatar", width=z["width"], vocab=z["vocab"],
+                            layers=(l, l, r, l, l, l, r, l), norm_eps=1e-5, block="sandwich", norm_kind="layer", loop_mix=False,
+                            logit_softcap=30.0, max_ctx=max_ctx, max_slots=max_slots)
+
+
+def device_tarudra_weights(spec: models.StackSpec, device, seed: int = 0) -> Dict[str, torch.Tensor]:
+    """Random Tarudra weights straight in the engine's layout on the device."""
+    g = torch.Generator(device=device).manual_seed(seed)
+    W = spec.width
+
+    def mat(*shape):
+        return (torch.randn(*shape, generator=g, device=device, dtype=torch.float32) * (shape[-1] ** -0.5)).to(torch.bfloat16)
+
+    def vec(n, centre=1.0, spread=0.05):
+        return centre + torch.randn(n, generator=g, device=device, dtype=torch.float32) * spread
+
+    w = {"embed": mat(spec.vocab, W), "head": mat(spec.vocab, W), "final_norm": vec(W)}
+    for i, L in enumerate(spec.layers):
+        lay, p = spec.mix_layout(i), f"l{i}."
+        w[p + "norm"], w[p + "post_norm"], w[p + "ff_norm"], w[p + "ff_post_norm"] = vec(W), vec(W, 0.6), vec(W), vec(W, 0.6)
+        w[p + "w_in"], w[p + "w_out"] = mat(lay.n_in, W), mat(W, lay.k_out)
+        if L.mixer == "attention":
+            w[p + "b_in"], w[p + "b_out"] = vec(lay.n_in, 0.0, 0.2), vec(W, 0.0, 0.2)
+        elif L.mixer == "latent_attention":
+            a = L.latent
+            w[p + "c_norm"], w[p + "q_norm"] = vec(a.kv_rank), vec(a.q_rank)
+            w[p + "uq"] = mat(a.heads * (a.dim + a.rot_dim), (a.q_rank + 7) // 8 * 8)
+            w[p + "uk"], w[p + "uv"] = mat(a.heads * a.dim, a.kv_rank), mat(a.heads * a.vdim, a.kv_rank)
+            w[p + "uk_t"] = w[p + "uk"].view(a.heads, a.dim, a.kv_rank).transpose(1, 2).contiguous()
+        else:
+            a = L.gdelta
+            w[p + "conv_w"] = vec(a.channels * a.conv, 0.0, 0.4)
+            w[p + "A_log"], w[p + "dt_bias"], w[p + "head_norm"] = vec(a.heads, 0.0, 0.5), vec(a.heads, -1.0, 0.5), vec(a.vdim)
+        w[p + "w_ff_in"], w[p + "w_ff_out"] = mat(L.ff, W), mat(W, L.ff)
+    return w
+
+
+def compare_tarudra(sizes: List[str], steps: int = 5, warmup: int = 3, prompt_len: int = 2048, n_decode: int = 32) -> dict:
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(dev)
+    timer = _Timer(dev)
+    max_ctx = prompt_len + n_decode + 8
+    rows = {}
+    for name in sizes:
+        def one(spec, weights):
+            eng = engine.DecodeEngine(spec, weights)
+            k = _measure(eng, True, prompt_len, n_decode, timer, steps, warmup, spec.vocab)
+            k["bytes_per_decode_token"] = eng.bytes_per_token(prompt_len)
+            k["launches_per_decode_token"] = eng.launches_per_token
+            k["matrix_params_per_token"] = spec.weight_params()
+            eng.close()
+            del eng
+            torch.cuda.empty_cache()
+            return k
+        tspec = tarudra_spec(name, max_ctx)
+        k = one(tspec, device_tarudra_weights(tspec, dev))
+        sspec = silatar_dense_beside(name, max_ctx)
+        l = one(sspec, device_silatar_weights(sspec, dev))
+        rows[name] = {"tarudra": k, "silatar_dense": l, "ratio": {m: round(k[m] / l[m], 3) for m in k if m.endswith("tok_s")}}
+    return {"metric": "tarudra_compare", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic", "prompt_len": prompt_len,
+            "decode_steps": n_decode, "steps": steps, "warmup": warmup, "l2": "flushed between timed iterations",
+            "sizes": rows}
+
+
+def main_tarudra(sizes: str, steps: int, warmup: int) -> None:
+    names = [s for s in sizes.split(",") if s] if sizes and sizes != "all" else list(TARUDRA_SIZES)
+    print(json.dumps(compare_tarudra(names, steps=steps, warmup=warmup)), flush=True)
+
+
 class _Timer:
     def __init__(self, device):
         self.device = device
